@@ -13,6 +13,8 @@ engine (`CacheManager.groups` says how many pages of which shape).
 * Pages are given back when the request ends (`release`), and, in a windowed
   group, as soon as every position they cover lies before the window of the next
   query (`commit`).
+* A run whose mixer is made of several mixers names several needs (`CacheSet`): member j of run r is entered under
+  the key (r, j) where a plain run is entered under r, its pages in the group of its need, its state among the states.
 * Every request also holds one slot of the fixed-size per-request state arrays
   (the reference's `gdn_state[l] : [S, ...]`, crates/mach-model/src/batched.rs:410-415),
   cleared when the request starts.  A model without such state still gets slots;
@@ -23,7 +25,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
-from ..parts.base import CacheNeed, FixedState, PagedCache
+from ..parts.base import CacheNeed, CacheSet, FixedState, PagedCache
 from .pool import Pool, PoolError
 
 
@@ -35,7 +37,7 @@ class OutOfPages(RuntimeError):
 class CacheGroup:
     index: int
     need: PagedCache
-    runs: List[int]  # entries of the run order that own a cache in this group
+    runs: List[Hashable]  # entries of the run order that own a cache in this group (r, or (r, j) for member j of a set)
     pool: Pool
 
 
@@ -61,10 +63,18 @@ class CacheManager:
             raise ValueError(f"page_size {page_size}")
         self.page_size = page_size
         self.groups: List[CacheGroup] = []
-        self.group_of_run: Dict[int, int] = {}
-        self.state_runs: Dict[int, FixedState] = {}
+        self.group_of_run: Dict[Hashable, int] = {}
+        self.state_runs: Dict[Hashable, FixedState] = {}
         by_need: Dict[PagedCache, int] = {}
-        for run, need in enumerate(needs):
+        flat = []
+        for r, need in enumerate(needs):
+            if isinstance(need, CacheSet):
+                if any(isinstance(n, CacheSet) for n in need.needs):
+                    raise TypeError(f"run {r}: a set of cache needs within a set")
+                flat += [((r, j), n) for j, n in enumerate(need.needs)]
+            else:
+                flat.append((r, need))
+        for run, need in flat:
             if isinstance(need, PagedCache):
                 if need not in by_need:
                     n = (pages_per_group or {}).get(len(self.groups), num_pages)

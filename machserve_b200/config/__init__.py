@@ -12,3 +12,4 @@ from .spec import LayerSpec, ModelSpec, PartSpec, RunSpec, part  # noqa: F401
 from .qwen2 import Qwen2Config  # noqa: F401
 from .venarax import VenaraxConfig  # noqa: F401
 from .fozutar import FozutarConfig  # noqa: F401
+from .modadra import ModadraConfig  # noqa: F401

@@ -54,6 +54,14 @@ class LayerSpec:
     mixer_norm: PartSpec
     feed_forward_norm: Optional[PartSpec]
     prefix: str
+    block_params: Mapping[str, Any] = field(default_factory=dict)  # constants of the arrangement itself (a multiplier of its adds)
+
+    def __post_init__(self):
+        object.__setattr__(self, "block_params", MappingProxyType(dict(self.block_params)))
+
+    def __hash__(self):
+        return hash((self.block, self.mixer, self.feed_forward, self.mixer_norm, self.feed_forward_norm, self.prefix,
+                     tuple(sorted((k, repr(v)) for k, v in self.block_params.items()))))
 
 
 @dataclass(frozen=True)

@@ -308,3 +308,21 @@ MS_API int ms_silu_mul(const void* gate_up, void* out, int dtype, int rows, int 
   MS_LAUNCH_CHECK("silu_mul");
   return 0;
 }
+
+// ------------------------------------------------------------------ soft cap
+
+// x <- cap * tanh(x / cap), in place, float32 (the logits of a head with a soft cap).
+__global__ void softcap_kernel(float* __restrict__ x, size_t total, float cap, float inv_cap) {
+  ms_pdl_trigger();
+  ms_pdl_wait();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < total) x[i] = cap * tanhf(x[i] * inv_cap);
+}
+
+MS_API int ms_softcap(float* x, long long total, float cap, cudaStream_t stream) {
+  if (total == 0) return 0;
+  MS_REQUIRE(total > 0 && cap > 0.f, "softcap: bad arguments total=%lld cap=%g", total, cap);
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  MS_LAUNCH_RESULT("softcap", ms_launch(softcap_kernel, dim3(blocks), dim3(256), 0, stream, 1, true, x, (size_t)total, cap, 1.f / cap));
+  return 0;
+}

@@ -110,3 +110,36 @@ MS_API int ms_sigmoid_gate_mul(const float* x, int ldx, const float* gate, int l
     MS_REQUIRE(false, "sigmoid_gate_mul: unknown out dtype %d", out_dtype);
   return 0;
 }
+
+// A sigmoid gate per head on a mixer's output: out[r, h*dv + c] = x[r, h*dv + c] * sigmoid(gate[r, h]).  x and out are of
+// one type (the type the next product reads) and may be the same array; gate is float32 with a row stride of its own (a
+// column range of a wider product).  The product is float32.
+template <typename T>
+__global__ void head_gate_mul_kernel(const T* x, const float* __restrict__ gate, int ldg, T* out, int heads, int dv, size_t total) {
+  ms_pdl_trigger();
+  ms_pdl_wait();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int n = heads * dv;
+  const size_t r = i / n;
+  const int h = (int)(i - r * n) / dv;
+  const float g = gate[r * ldg + h];
+  out[i] = ms_from_float<T>(ms_to_float(x[i]) / (1.f + expf(-g)));
+}
+
+MS_API int ms_head_gate_mul(const void* x, const float* gate, int ldg, void* out, int dtype, int rows, int heads, int dv,
+                            cudaStream_t stream) {
+  if (rows == 0) return 0;
+  MS_REQUIRE(rows > 0 && heads > 0 && dv > 0 && ldg >= heads, "head_gate_mul: bad sizes rows=%d heads=%d dv=%d", rows, heads, dv);
+  const size_t total = (size_t)rows * heads * dv;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  if (dtype == MS_F32)
+    MS_LAUNCH_RESULT("head_gate_mul", ms_launch(head_gate_mul_kernel<float>, dim3(blocks), dim3(256), 0, stream, 1, true, (const float*)x, gate,
+                                                ldg, (float*)out, heads, dv, total));
+  else if (dtype == MS_BF16)
+    MS_LAUNCH_RESULT("head_gate_mul", ms_launch(head_gate_mul_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, 1, true,
+                                                (const __nv_bfloat16*)x, gate, ldg, (__nv_bfloat16*)out, heads, dv, total));
+  else
+    MS_REQUIRE(false, "head_gate_mul: unknown dtype %d", dtype);
+  return 0;
+}

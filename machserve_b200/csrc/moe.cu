@@ -3,6 +3,10 @@
 //   route:    of a token's E router logits (float32, plus the router's bias) the `top` largest are chosen (the lower index wins a tie); their
 //             weights are the softmax over the chosen logits only.  ids int32 [T, top], weights float32 [T, top], in
 //             descending order of the logits.  One warp a token.
+//   route_scored: the other way to choose: scores s = sigmoid(logit); an expert is chosen by s + correction (a learned
+//             number per expert that enters the choice only), among the experts of the best `keep` of `count` equal groups
+//             of neighbours (a group's score: the sum of its two largest choice scores; the rest count as minus infinity);
+//             the weights are the chosen experts' s over their sum (+ 1e-20), times `scale`.  One warp a token.
 //   gate_up:  h[p, n] = act(Wg[e_p][n, :] . x[t_p, :]) * (Wu[e_p][n, :] . x[t_p, :]) for pair p = (token t_p, its j-th expert e_p)
 //   down:     y[t, n] = sum_j weight[t, j] * (Wd[e_(t,j)][n, :] . h[(t, j), :]), j ascending
 // The pair kernels stream the chosen experts' weights once per pair: what decoding rows want (a token reads only
@@ -70,8 +74,97 @@ MS_API int ms_moe_route(const float* logits, const float* bias, int experts, int
   return 0;
 }
 
+// One warp a token; per warp in shared memory: the choice scores [experts], the groups' scores [count].
+__global__ void __launch_bounds__(128)
+moe_route_scored_kernel(const float* __restrict__ logits, const float* __restrict__ correction, int experts, int top, int count, int keep,
+                        float scale, int* __restrict__ ids, float* __restrict__ weights, int tokens) {
+  extern __shared__ float mr_smem[];
+  ms_pdl_trigger();
+  ms_pdl_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (t >= tokens) return;
+  float* choice = mr_smem + (size_t)warp * (experts + count);
+  float* gscore = choice + experts;
+  const float* z = logits + (size_t)t * experts;
+  for (int e = lane; e < experts; e += 32) choice[e] = 1.f / (1.f + expf(-z[e])) + (correction ? correction[e] : 0.f);
+  __syncwarp();
+  const int per = experts / count;
+  if (keep < count) {
+    for (int g = lane; g < count; g += 32) {  // the sum of the group's two largest choice scores
+      float a = -INFINITY, b = -INFINITY;
+      for (int e = g * per; e < (g + 1) * per; ++e) {
+        const float v = choice[e];
+        if (v > a) { b = a; a = v; } else if (v > b) { b = v; }
+      }
+      gscore[g] = per > 1 ? a + b : a;
+    }
+    __syncwarp();
+    // a group is kept if fewer than `keep` groups come before it in the order (larger score first, lower index first among equals)
+    for (int g = lane; g < count; g += 32) {
+      const float v = gscore[g];
+      int before = 0;
+      for (int o = 0; o < count; ++o) before += gscore[o] > v || (gscore[o] == v && o < g);
+      if (before >= keep)
+        for (int e = g * per; e < (g + 1) * per; ++e) choice[e] = -INFINITY;
+    }
+    __syncwarp();
+  }
+  float last_v = INFINITY, sum = 0.f;
+  int last_i = -1;
+  for (int j = 0; j < top; ++j) {
+    float best = -INFINITY;
+    int best_i = 0x7fffffff;
+    for (int e = lane; e < experts; e += 32) {
+      const float v = choice[e];
+      const bool after = v < last_v || (v == last_v && e > last_i);
+      if (after && (v > best || (v == best && e < best_i))) {
+        best = v;
+        best_i = e;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+      if (ov > best || (ov == best && oi < best_i)) {
+        best = ov;
+        best_i = oi;
+      }
+    }
+    if (best_i >= experts) best_i = 0;  // (fewer experts are allowed than a token is to choose: checked on the host)
+    const float w = 1.f / (1.f + expf(-z[best_i]));  // the weight is the score without the correction
+    sum += w;
+    if (lane == 0) {
+      ids[(size_t)t * top + j] = best_i;
+      weights[(size_t)t * top + j] = w;
+    }
+    last_v = best;
+    last_i = best_i;
+  }
+  __syncwarp();
+  if (lane == 0)
+    for (int j = 0; j < top; ++j) weights[(size_t)t * top + j] = weights[(size_t)t * top + j] / (sum + 1e-20f) * scale;
+}
+
+// logits float32 [tokens, experts]; correction float32 [experts] or null; count groups of experts / count neighbours, keep of them
+MS_API int ms_moe_route_scored(const float* logits, const float* correction, int experts, int top, int count, int keep, float scale,
+                               int* ids, float* weights, int tokens, cudaStream_t stream) {
+  if (tokens == 0) return 0;
+  MS_REQUIRE(tokens > 0 && experts > 0 && top > 0 && count > 0 && keep > 0 && keep <= count && experts % count == 0,
+             "moe_route_scored: bad arguments tokens=%d experts=%d top=%d groups=%d keep=%d", tokens, experts, top, count, keep);
+  MS_REQUIRE(top <= experts / count * keep, "moe_route_scored: %d experts a token, but only %d are in the %d kept groups", top,
+             experts / count * keep, keep);
+  const size_t smem = (size_t)4 * (experts + count) * sizeof(float);
+  MS_REQUIRE(smem <= 48 * 1024, "moe_route_scored: %d experts are more than the kernel covers", experts);
+  MS_LAUNCH_RESULT("moe_route_scored", ms_launch(moe_route_scored_kernel, dim3((tokens + 3) / 4), dim3(128), smem, stream, 1, true, logits,
+                                                 correction, experts, top, count, keep, scale, ids, weights, tokens));
+  return 0;
+}
+
 __device__ __forceinline__ float moe_act(float g, int act) {
   if (act == 0) return g / (1.f + expf(-g));
+  if (act == 2) return 0.5f * g * (1.f + erff(g * 0.7071067811865476f));  // the exact GELU
   return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
 }
 
@@ -116,22 +209,22 @@ moe_gate_up_pairs_kernel(const T* __restrict__ x, const T* __restrict__ wg, cons
   int e = ids[pair];
   e = e < 0 ? 0 : (e >= experts ? experts - 1 : e);
   const T* g = wg + ((size_t)e * ff + n) * d;
-  const T* u = wu + ((size_t)e * ff + n) * d;
+  const T* u = wu ? wu + ((size_t)e * ff + n) * d : nullptr;  // (no second matrix: experts without a gate, h = act(Wg x))
   float sg = 0.f, su = 0.f;
   if (vec) {  // (the order of a sum depends on d and on this flag, which depends on d and the pointers' alignment alone)
     for (int c = lane * 8; c < d; c += 256) {
       sg = moe_dot8(g + c, moe_x + c, sg);
-      su = moe_dot8(u + c, moe_x + c, su);
+      if (u) su = moe_dot8(u + c, moe_x + c, su);
     }
   } else {
     for (int c = lane; c < d; c += 32) {
       const float xv = moe_x[c];
       sg = fmaf(ms_to_float(g[c]), xv, sg);
-      su = fmaf(ms_to_float(u[c]), xv, su);
+      if (u) su = fmaf(ms_to_float(u[c]), xv, su);
     }
   }
   sg = ms_warp_sum(sg);
-  su = ms_warp_sum(su);
+  su = u ? ms_warp_sum(su) : 1.f;
   if (lane == 0) h[(size_t)pair * ff + n] = ms_from_float<T>(moe_act(sg, act) * su);
 }
 
@@ -175,11 +268,11 @@ moe_down_pairs_kernel(const T* __restrict__ h, const T* __restrict__ wd, const i
 MS_API int ms_moe_gate_up_pairs(const void* x, const void* wg, const void* wu, const int* ids, const int* slots, void* h, int dtype,
                                 int tokens, int top, int d, int ff, int experts, int act, cudaStream_t stream) {
   if (tokens == 0) return 0;
-  MS_REQUIRE(tokens > 0 && top > 0 && d > 0 && ff > 0 && experts > 0 && (act == 0 || act == 1), "moe_gate_up_pairs: bad arguments");
+  MS_REQUIRE(tokens > 0 && top > 0 && d > 0 && ff > 0 && experts > 0 && act >= 0 && act <= 2, "moe_gate_up_pairs: bad arguments");
   MS_REQUIRE((long long)tokens * top <= 65535, "moe_gate_up_pairs: %d pairs are more than one launch takes", tokens * top);
   MS_REQUIRE((size_t)d * 4 <= 48 * 1024, "moe_gate_up_pairs: rows of %d are too wide", d);
   const dim3 grid((ff + MOE_WARPS - 1) / MOE_WARPS, tokens * top), block(MOE_WARPS * 32);
-  const int vec = d % 8 == 0 && ((uintptr_t)wg | (uintptr_t)wu) % 32 == 0;
+  const int vec = d % 8 == 0 && ((uintptr_t)wg | (uintptr_t)wu) % 32 == 0;  // (wu may be null: experts without a gate)
   if (dtype == MS_F32)
     MS_LAUNCH_RESULT("moe_gate_up_pairs", ms_launch(moe_gate_up_pairs_kernel<float>, grid, block, (size_t)d * 4, stream, 1, true, (const float*)x,
                                                     (const float*)wg, (const float*)wu, ids, slots, (float*)h, top, d, ff, experts, act, vec));

@@ -59,15 +59,20 @@ moe_sort_kernel(const int* __restrict__ ids, const int* __restrict__ slots, int 
 
 __device__ __forceinline__ float mg_act(float g, int act) {
   if (act == 0) return g / (1.f + expf(-g));
+  if (act == 2) return 0.5f * g * (1.f + erff(g * 0.7071067811865476f));  // the exact GELU
   return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
 }
 
-template <bool GATED>
+// MODE 0: the second product (rows: the sorted h; one matrix; float32 results to the pairs' own rows).  MODE 1: the first
+// product of gated experts (rows gathered from the tokens; two matrices; h = act(gate) * up).  MODE 2: the first product of
+// experts without a gate (rows gathered; one matrix; h = act(up)).
+template <int MODE>
 __global__ void __launch_bounds__(128)
 moe_grouped_kernel(const __nv_bfloat16* __restrict__ a, int lda, const int* __restrict__ order, int top,
                    const __nv_bfloat16* __restrict__ b0, const __nv_bfloat16* __restrict__ b1, int n, int k,
                    const int* __restrict__ tile_expert, const int* __restrict__ tile_row0, const int* __restrict__ offsets,
                    const int* __restrict__ num_tiles, __nv_bfloat16* __restrict__ h, float* __restrict__ z, int act) {
+  constexpr bool GATED = MODE == 1, FIRST = MODE != 0;
   constexpr int NB = GATED ? 2 : 1;
   extern __shared__ __align__(16) unsigned char mg_smem[];
   typedef __nv_bfloat16 (*ATile)[MG_BM][MG_LD];
@@ -95,7 +100,7 @@ moe_grouped_kernel(const __nv_bfloat16* __restrict__ a, int lda, const int* __re
   for (int i = 0; i < 4; ++i) {
     const int r = r_a + 32 * i;
     ok_a[i] = r < rows;
-    const size_t arow = ok_a[i] ? (GATED ? (size_t)(row_of[r] / top) : (size_t)(row0 + r)) : 0;
+    const size_t arow = ok_a[i] ? (FIRST ? (size_t)(row_of[r] / top) : (size_t)(row0 + r)) : 0;
     src_a[i] = a + arow * lda + ch * 8;
   }
 #pragma unroll
@@ -174,6 +179,8 @@ moe_grouped_kernel(const __nv_bfloat16* __restrict__ a, int lda, const int* __re
           if (col >= n) continue;
           if (GATED)
             h[(size_t)(row0 + r) * n + col] = __float2bfloat16_rn(mg_act(acc[0][t][j][2 * half + c], act) * acc[NB - 1][t][j][2 * half + c]);
+          else if (FIRST)
+            h[(size_t)(row0 + r) * n + col] = __float2bfloat16_rn(mg_act(acc[0][t][j][2 * half + c], act));
           else
             z[(size_t)row_of[r] * n + col] = acc[0][t][j][2 * half + c];
         }
@@ -212,7 +219,7 @@ MS_API int ms_moe_grouped(const void* x, const void* wg, const void* wu, const v
                           const int* slots, int* scratch, void* h, float* z, float* y, int tokens, int top, int d, int ff, int experts,
                           int act, cudaStream_t stream) {
   if (tokens == 0) return 0;
-  MS_REQUIRE(tokens > 0 && top > 0 && (act == 0 || act == 1), "moe_grouped: bad arguments");
+  MS_REQUIRE(tokens > 0 && top > 0 && act >= 0 && act <= 2, "moe_grouped: bad arguments");
   MS_REQUIRE(ms_moe_grouped_supports(d, ff, experts), "moe_grouped: sizes d=%d ff=%d experts=%d are not covered", d, ff, experts);
   const int pairs = tokens * top;
   const int max_tiles = pairs / MG_BM + experts;
@@ -227,16 +234,24 @@ MS_API int ms_moe_grouped(const void* x, const void* wg, const void* wu, const v
   const __nv_bfloat16* xb = (const __nv_bfloat16*)x;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e1 = cudaFuncSetAttribute(moe_grouped_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)mg_smem_bytes(true));
-    cudaError_t e2 = cudaFuncSetAttribute(moe_grouped_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)mg_smem_bytes(false));
+    cudaError_t e1 = cudaFuncSetAttribute(moe_grouped_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)mg_smem_bytes(true));
+    cudaError_t e2 = cudaFuncSetAttribute(moe_grouped_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)mg_smem_bytes(false));
+    if (e2 == cudaSuccess)
+      e2 = cudaFuncSetAttribute(moe_grouped_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)mg_smem_bytes(false));
     MS_REQUIRE(e1 == cudaSuccess && e2 == cudaSuccess, "moe_grouped: cannot get shared memory: %s", cudaGetErrorString(e1 != cudaSuccess ? e1 : e2));
     configured = true;
   }
-  MS_LAUNCH_RESULT("moe_grouped", ms_launch(moe_grouped_kernel<true>, dim3((ff + MG_BN - 1) / MG_BN, max_tiles), dim3(128), mg_smem_bytes(true), stream, 1, true,
-                                            xb, d, (const int*)order, top, (const __nv_bfloat16*)wg, (const __nv_bfloat16*)wu, ff, d,
-                                            (const int*)tile_expert, (const int*)tile_row0, (const int*)offsets, (const int*)num_tiles,
-                                            (__nv_bfloat16*)h, (float*)nullptr, act));
-  MS_LAUNCH_RESULT("moe_grouped", ms_launch(moe_grouped_kernel<false>, dim3((d + MG_BN - 1) / MG_BN, max_tiles), dim3(128), mg_smem_bytes(false), stream, 1, true,
+  if (wu)
+    MS_LAUNCH_RESULT("moe_grouped", ms_launch(moe_grouped_kernel<1>, dim3((ff + MG_BN - 1) / MG_BN, max_tiles), dim3(128), mg_smem_bytes(true), stream, 1, true,
+                                              xb, d, (const int*)order, top, (const __nv_bfloat16*)wg, (const __nv_bfloat16*)wu, ff, d,
+                                              (const int*)tile_expert, (const int*)tile_row0, (const int*)offsets, (const int*)num_tiles,
+                                              (__nv_bfloat16*)h, (float*)nullptr, act));
+  else  // experts without a gate: wg is their one input matrix
+    MS_LAUNCH_RESULT("moe_grouped", ms_launch(moe_grouped_kernel<2>, dim3((ff + MG_BN - 1) / MG_BN, max_tiles), dim3(128), mg_smem_bytes(false), stream, 1, true,
+                                              xb, d, (const int*)order, top, (const __nv_bfloat16*)wg, (const __nv_bfloat16*)nullptr, ff, d,
+                                              (const int*)tile_expert, (const int*)tile_row0, (const int*)offsets, (const int*)num_tiles,
+                                              (__nv_bfloat16*)h, (float*)nullptr, act));
+  MS_LAUNCH_RESULT("moe_grouped", ms_launch(moe_grouped_kernel<0>, dim3((d + MG_BN - 1) / MG_BN, max_tiles), dim3(128), mg_smem_bytes(false), stream, 1, true,
                                             (const __nv_bfloat16*)h, ff, (const int*)order, top, (const __nv_bfloat16*)wd,
                                             (const __nv_bfloat16*)nullptr, d, ff, (const int*)tile_expert, (const int*)tile_row0,
                                             (const int*)offsets, (const int*)num_tiles, (__nv_bfloat16*)nullptr, z, act));

@@ -1,12 +1,15 @@
 // Kernels around the residual stream for layers whose two halves are summed before they are added, with an RMS norm:
 //
 // * embed_scaled_pos: x[r, :] = E[token[r], :] * scale + P[position[r], :] in float32 (P a learned table, or none);
-// * add_streams_rmsnorm: x <- x + ((a + b) + first + vec), then, when a weight is given, out = x / rms(x) * w.
+// * add_streams_rmsnorm: x <- x + (m * (a + b) + first + vec), then, when a weight is given, out = x / rms(x) * w
+//   (m: a multiplier of the deltas, 1 for most layers).
 //   a, b: deltas of the step's rows (float32 or bfloat16, either may be absent); first: another float32 stream
 //   [T, d] (the embedding's output, for the start of a pass over looped layers); vec: one float32 row added to
 //   every row.  Without a weight the kernel only adds (the entry of a pass).  With `rows`, output row i is made
 //   from input row rows[i] and nothing is written back (the final norm of the wanted rows).
 //   The sums and the norm are float32; the order of a row's additions depends on d alone.
+// * norm_pair_mean: out = m * (a / rms(a) * wa + b / rms(b) * wb), each rms over the row's d elements with eps inside the
+//   root: the two halves of a mixer made of two, each normed with a weight of its own, in float32.
 // * gated_act_mul: out[r, c] = act(gate_up[r, c]) * gate_up[r, inter + c], act = SiLU or the tanh form of GELU,
 //   computed in float32 from a float32 or bfloat16 product.
 #include "launch.cuh"
@@ -82,7 +85,8 @@ template <typename TO, bool VEC>
 __global__ void __launch_bounds__(ST_THREADS)
 add_streams_rmsnorm_kernel(float* __restrict__ residual, const void* __restrict__ a, int a_dtype, const void* __restrict__ b,
                            int b_dtype, const float* __restrict__ first, const float* __restrict__ vec,
-                           const float* __restrict__ weight, TO* __restrict__ out, const int* __restrict__ rows, int d, float eps) {
+                           const float* __restrict__ weight, TO* __restrict__ out, const int* __restrict__ rows, int d, float eps,
+                           float m) {
   __shared__ float scratch[33];
   ms_pdl_trigger();
   ms_pdl_wait();
@@ -105,8 +109,8 @@ add_streams_rmsnorm_kernel(float* __restrict__ residual, const void* __restrict_
         const float4 tb = b ? st_load4(b, b_dtype, base + 4 * g) : zero;
         const float4 tf = first ? *reinterpret_cast<const float4*>(first + base + 4 * g) : zero;
         const float4 tv = vec ? *reinterpret_cast<const float4*>(vec + 4 * g) : zero;
-        float4 s = make_float4(((ta.x + tb.x) + tf.x) + tv.x, ((ta.y + tb.y) + tf.y) + tv.y, ((ta.z + tb.z) + tf.z) + tv.z,
-                               ((ta.w + tb.w) + tf.w) + tv.w);
+        float4 s = make_float4(((ta.x + tb.x) * m + tf.x) + tv.x, ((ta.y + tb.y) * m + tf.y) + tv.y, ((ta.z + tb.z) * m + tf.z) + tv.z,
+                               ((ta.w + tb.w) * m + tf.w) + tv.w);
         x.x += s.x; x.y += s.y; x.z += s.z; x.w += s.w;
         if (adds && !rows) *reinterpret_cast<float4*>(residual + base + 4 * g) = x;
         v[i] = x;
@@ -130,6 +134,7 @@ add_streams_rmsnorm_kernel(float* __restrict__ residual, const void* __restrict_
       float s = 0.f;
       if (a) s = st_load1(a, a_dtype, base + c);
       if (b) s += st_load1(b, b_dtype, base + c);
+      s *= m;
       if (first) s += first[base + c];
       if (vec) s += vec[c];
       return residual[base + c] + s;
@@ -153,7 +158,7 @@ add_streams_rmsnorm_kernel(float* __restrict__ residual, const void* __restrict_
 
 MS_API int ms_add_streams_rmsnorm(float* residual, const void* a, int a_dtype, const void* b, int b_dtype, const float* first,
                                   const float* vec, const float* weight, void* out, int out_dtype, const int* rows, int n_out, int d,
-                                  float eps, cudaStream_t stream) {
+                                  float eps, float delta_scale, cudaStream_t stream) {
   if (n_out == 0) return 0;
   MS_REQUIRE(n_out > 0 && d > 0, "add_streams_rmsnorm: bad sizes n_out=%d d=%d", n_out, d);
   MS_REQUIRE((a_dtype == MS_F32 || a_dtype == MS_BF16) && (b_dtype == MS_F32 || b_dtype == MS_BF16), "add_streams_rmsnorm: bad delta dtype");
@@ -162,7 +167,8 @@ MS_API int ms_add_streams_rmsnorm(float* residual, const void* a, int a_dtype, c
   const bool vecs = d % 4 == 0 && d <= 4 * ST_THREADS * ST_KEEP && all % 16 == 0;
 #define MS_ST_LAUNCH(TO, V)                                                                                                       \
   MS_LAUNCH_RESULT("add_streams_rmsnorm", ms_launch(add_streams_rmsnorm_kernel<TO, V>, dim3(n_out), dim3(ST_THREADS), 0, stream, 1, \
-                                                    true, residual, a, a_dtype, b, b_dtype, first, vec, weight, (TO*)out, rows, d, eps))
+                                                    true, residual, a, a_dtype, b, b_dtype, first, vec, weight, (TO*)out, rows, d, eps,     \
+                                                    delta_scale))
   if (out_dtype == MS_BF16) {
     if (vecs) MS_ST_LAUNCH(__nv_bfloat16, true);
     else MS_ST_LAUNCH(__nv_bfloat16, false);
@@ -178,8 +184,40 @@ MS_API int ms_add_streams_rmsnorm(float* residual, const void* a, int a_dtype, c
 
 // ------------------------------------------------------------------------------------------------------------------
 
+// One block a row; a and b float32 [rows, d]; the row's two sums of squares are taken side by side.
+__global__ void __launch_bounds__(ST_THREADS)
+norm_pair_mean_kernel(const float* __restrict__ a, const float* __restrict__ b, const float* __restrict__ wa, const float* __restrict__ wb,
+                      float* __restrict__ out, int d, float eps, float m) {
+  __shared__ float scratch_a[33], scratch_b[33];
+  ms_pdl_trigger();
+  ms_pdl_wait();
+  const size_t base = (size_t)blockIdx.x * d;
+  float sa = 0.f, sb = 0.f;
+  for (int c = threadIdx.x; c < d; c += blockDim.x) {
+    const float x = a[base + c], y = b[base + c];
+    sa += x * x;
+    sb += y * y;
+  }
+  sa = ms_block_sum(sa, scratch_a);
+  sb = ms_block_sum(sb, scratch_b);
+  const float ia = rsqrtf(sa / (float)d + eps), ib = rsqrtf(sb / (float)d + eps);
+  for (int c = threadIdx.x; c < d; c += blockDim.x) out[base + c] = m * (a[base + c] * ia * wa[c] + b[base + c] * ib * wb[c]);
+}
+
+MS_API int ms_norm_pair_mean(const float* a, const float* b, const float* wa, const float* wb, float* out, int rows, int d, float eps,
+                             float m, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  MS_REQUIRE(rows > 0 && d > 0, "norm_pair_mean: bad sizes rows=%d d=%d", rows, d);
+  MS_LAUNCH_RESULT("norm_pair_mean", ms_launch(norm_pair_mean_kernel, dim3(rows), dim3(ST_THREADS), 0, stream, 1, true, a, b, wa, wb, out, d,
+                                               eps, m));
+  return 0;
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+
 __device__ __forceinline__ float st_act(float g, int act) {
   if (act == 0) return g / (1.f + expf(-g));
+  if (act == 2) return 0.5f * g * (1.f + erff(g * 0.7071067811865476f));  // the exact GELU
   // 0.5 g (1 + tanh(u)) = g / (1 + exp(-2u)): one accurate exponential and one division
   const float u = 0.7978845608028654f * (g + 0.044715f * g * g * g);
   return g / (1.f + expf(-2.f * u));
@@ -210,7 +248,7 @@ __global__ void gated_act_mul_kernel(const TI* __restrict__ gate_up, TO* __restr
   out[(size_t)row * inter + c] = ms_from_float<TO>(st_act(ms_to_float(p[c]), act) * ms_to_float(p[inter + c]));
 }
 
-// act: 0 SiLU, 1 GELU (tanh form).  gate_up [rows, 2*inter] float32 or bfloat16, out [rows, inter] float32 or bfloat16.
+// act: 0 SiLU, 1 GELU (tanh form), 2 GELU (exact).  gate_up [rows, 2*inter] float32 or bfloat16, out [rows, inter] float32 or bfloat16.
 // Eight columns a thread with 16-byte accesses: bfloat16 in and out, widths that are a multiple of 8.
 __global__ void gated_act_mul_vec8_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out, int inter, int act) {
   ms_pdl_trigger();
@@ -234,7 +272,7 @@ __global__ void gated_act_mul_vec8_kernel(const __nv_bfloat16* __restrict__ gate
 
 MS_API int ms_gated_act_mul(const void* gate_up, int in_dtype, void* out, int out_dtype, int rows, int inter, int act, cudaStream_t stream) {
   if (rows == 0) return 0;
-  MS_REQUIRE(rows > 0 && rows <= 65535 * 64 && inter > 0 && (act == 0 || act == 1), "gated_act_mul: bad arguments rows=%d inter=%d act=%d", rows,
+  MS_REQUIRE(rows > 0 && rows <= 65535 * 64 && inter > 0 && act >= 0 && act <= 2, "gated_act_mul: bad arguments rows=%d inter=%d act=%d", rows,
              inter, act);
   MS_REQUIRE(rows <= 65535, "gated_act_mul: %d rows are more than one launch takes", rows);
   if (in_dtype == MS_BF16 && out_dtype == MS_BF16 && inter % 8 == 0 && ((uintptr_t)gate_up | (uintptr_t)out) % 16 == 0) {

@@ -26,7 +26,7 @@ from .. import ops
 from ..cache import CacheManager, OutOfPages
 from ..config import ModelConfig, load_config
 from ..parts import DecoderModel, FixedState, PagedBinding, Runtime, StateBinding, StepContext, Workspace
-from ..parts.base import StepShape, Work
+from ..parts.base import CacheSet, StepShape, Work
 from ..weights import load_weights, random_tensors, random_tensors_on_device
 
 _DTYPES = {
@@ -152,7 +152,7 @@ class ModelRunner:
                 for pl in g.need.planes
             })
             self.tables.append(torch.full((max_requests, self.max_pages), -1, dtype=torch.int32, device=self.device))
-        self.states: Dict[int, torch.Tensor] = {
+        self.states: Dict[Hashable, torch.Tensor] = {
             run: torch.zeros((max_requests, *need.shape), dtype=torch.float32, device=self.device)
             for run, need in self.cache.state_runs.items()
         }
@@ -217,17 +217,23 @@ class ModelRunner:
         return cls(config, random_tensors(model.tensors(), seed, dt), dtype=dt, **kw)
 
     def _make_bindings(self):
-        out = []
-        for i, run in enumerate(self.spec.run_order):
-            owner = i if run.cache_of is None else run.cache_of
+        def binding(owner):
             if owner in self.cache.group_of_run:
                 g = self.cache.group_of_run[owner]
                 j = self.cache.groups[g].runs.index(owner)
-                out.append(PagedBinding(g, {name: arr[j] for name, arr in self.pages[g].items()}, self.cache.groups[g].need.window))
-            elif owner in self.states:
-                out.append(StateBinding(self.states[owner]))
+                return PagedBinding(g, {name: arr[j] for name, arr in self.pages[g].items()}, self.cache.groups[g].need.window)
+            if owner in self.states:
+                return StateBinding(self.states[owner])
+            return None
+
+        out = []
+        for i, run in enumerate(self.spec.run_order):
+            owner = i if run.cache_of is None else run.cache_of
+            need = self.model.blocks[self.spec.run_order[owner].layer].mixer.cache_need()
+            if isinstance(need, CacheSet):  # a mixer made of several: one binding per member, in their order
+                out.append(tuple(binding((owner, j)) for j in range(len(need.needs))))
             else:
-                out.append(None)
+                out.append(binding(owner))
         return out
 
     # -------------------------------------------------------------------- step

@@ -127,7 +127,15 @@ class _Signatures:
     ms_qk_norm_store = [P, I, P, P, F, F, I, P, P, P, I, I, I, P, P, P, P, I, I, I, I, I, I, I, P]
     ms_latent_encode = [P, I, I, P, F, P, I, I, P, P, P, I, I, I, P, P, I, P, I, I, I, I, I, I, I, P]
     ms_embed_scaled_pos = [P, I, P, P, P, P, I, I, I, I, F, P]
-    ms_add_streams_rmsnorm = [P, P, I, P, I, P, P, P, P, I, P, I, I, F, P]
+    ms_add_streams_rmsnorm = [P, P, I, P, I, P, P, P, P, I, P, I, I, F, F, P]
+    ms_norm_pair_mean = [P, P, P, P, P, I, I, F, F, P]
+    ms_softcap = [P, LL, F, P]
+    ms_head_gate_mul = [P, P, I, P, I, I, I, I, P]
+    ms_rope_store = [P, I, P, I, I, I, P, P, P, I, I, I, P, P, P, P, I, I, I, I, I, I, I, P]
+    ms_gdr_prepare = [P, I, I, I, I, P, I, P, P, P, LL, LL, P, P, P, P, P, I, I, I, I, I, F, P]
+    ms_gdr_conv_update = [P, I, I, I, P, LL, LL, P, P, P, I, I, P]
+    ms_gdr_scan = [P, P, P, LL, P, P, P, P, I, I, I, I, I, I, P]
+    ms_moe_route_scored = [P, P, I, I, I, I, F, P, P, I, P]
     ms_gated_act_mul = [P, I, P, I, I, I, I, P]
     ms_head_norm_store = [P, I, P, P, P, F, I, P, P, P, I, I, I, P, P, P, P, I, I, I, I, I, I, I, I, P]
     ms_attention_wide_scored = [P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, F, P, I, I, I, P]
@@ -1201,8 +1209,8 @@ def embed_scaled_pos(table, ids, positions, pos_table, out, scale: float):
     return out
 
 
-def add_streams_rmsnorm(residual, delta_a, delta_b, first, vec, weight, out, eps: float = 0.0, rows=None):
-    """residual += (delta_a + delta_b) + first + vec (each may be None), then, with `weight`, out = residual / rms * weight.
+def add_streams_rmsnorm(residual, delta_a, delta_b, first, vec, weight, out, eps: float = 0.0, rows=None, delta_scale: float = 1.0):
+    """residual += delta_scale * (delta_a + delta_b) + first + vec (each may be None), then, with `weight`, out = residual / rms * weight.
     With `rows`, output row i comes from input row rows[i] and nothing is written back.  residual, first float32 [T, d];
     deltas [T, d] float32 or bfloat16; vec, weight float32 [d]; out [n_out, d] float32 or bfloat16 (None without a weight)."""
     t, d = residual.shape
@@ -1224,12 +1232,13 @@ def add_streams_rmsnorm(residual, delta_a, delta_b, first, vec, weight, out, eps
         else:
             _need(rows.dtype == torch.int32 and rows.numel() >= n_out, "add_streams_rmsnorm: bad row list")
     _check(lib().ms_add_streams_rmsnorm(_ptr(residual), *_delta_args(delta_a), *_delta_args(delta_b), _ptr(first), _ptr(vec), _ptr(weight),
-                                        _ptr(out), _code(out) if out is not None else F32, _ptr(rows), n_out, d, float(eps), _stream()),
+                                        _ptr(out), _code(out) if out is not None else F32, _ptr(rows), n_out, d, float(eps), float(delta_scale),
+                                        _stream()),
            "add_streams_rmsnorm")
     return out
 
 
-ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "gelu": 2}  # "gelu": the exact form, 0.5 z (1 + erf(z / sqrt(2)))
 
 
 def gated_act_mul(gate_up, out, activation: str):
@@ -1323,6 +1332,112 @@ def gla_output(o, gate, weight, eps: float, out, heads: int, dv: int):
     return out
 
 
+# ---------------------------------------------- a mixer of two halves: rotation with a cache of unequal widths, head gates, the gated delta rule
+
+
+def norm_pair_mean(a, b, wa, wb, out, eps: float, scale: float = 0.5):
+    """out = scale * (a / rms(a) * wa + b / rms(b) * wb), each root mean square over the row (eps inside the root), in float32.
+    a, b, out float32 [T, d]; wa, wb float32 [d]."""
+    t, d = out.shape
+    _need(all(x.dtype == torch.float32 and x.is_contiguous() and tuple(x.shape) == (t, d) for x in (a, b, out)), "norm_pair_mean: bad rows")
+    _need(all(w.dtype == torch.float32 and w.is_contiguous() and w.numel() == d for w in (wa, wb)), "norm_pair_mean: bad weights")
+    _check(lib().ms_norm_pair_mean(_ptr(a), _ptr(b), _ptr(wa), _ptr(wb), _ptr(out), t, d, float(eps), float(scale), _stream()), "norm_pair_mean")
+    return out
+
+
+def softcap(x, cap: float):
+    """x <- cap * tanh(x / cap) in place; x float32, contiguous."""
+    _need(x.dtype == torch.float32 and x.is_contiguous(), "softcap: bad tensor")
+    _check(lib().ms_softcap(_ptr(x), x.numel(), float(cap), _stream()), "softcap")
+    return x
+
+
+def head_gate_mul(x, gate, out, heads: int, dv: int):
+    """out[r, h*dv + c] = x[r, h*dv + c] * sigmoid(gate[r, h]).  x, out [T, heads*dv] of one dtype (they may be the same tensor);
+    gate float32 [T, heads] with unit column stride (any row stride)."""
+    t = x.shape[0]
+    _need(x.is_contiguous() and out.is_contiguous() and x.dtype == out.dtype and tuple(x.shape) == (t, heads * dv)
+          and tuple(out.shape) == (t, heads * dv), "head_gate_mul: bad rows")
+    _need(gate.dtype == torch.float32 and gate.stride(1) == 1 and tuple(gate.shape) == (t, heads), "head_gate_mul: bad gate")
+    _check(lib().ms_head_gate_mul(_ptr(x), _ptr(gate), gate.stride(0), _ptr(out), _code(x), t, heads, dv, _stream()), "head_gate_mul")
+    return out
+
+
+def rope_store(proj, cos_sin, rot: int, interleaved: bool, positions, slot_of_token, block_table, q_out, k_pages, v_pages, num_heads: int,
+               num_kv_heads: int, dk: int, dv: int, store: bool = True, q_half=None):
+    """The first `rot` coordinates of every query and key head turned by the table's angles at the row's position (pairs
+    (i, i + rot/2), or (2i, 2i + 1) when `interleaved`); q to q_out (float32 [T, Hq*dk]) and, optionally, to a bfloat16 copy;
+    the turned keys into k_pages [pages, Hkv, page, dk] and the values into v_pages [pages, Hkv, page, dv].  proj float32
+    [T, >= Hq*dk + Hkv*(dk + dv)] = [q | k | v]; cos_sin float32 [positions, rot/2, 2] (None when rot is 0)."""
+    t = q_out.shape[0]
+    _need(proj.dtype == torch.float32 and proj.stride(1) == 1 and q_out.dtype == torch.float32 and q_out.is_contiguous()
+          and q_out.numel() == t * num_heads * dk, "rope_store: bad layout")
+    _need(q_half is None or (q_half.dtype == torch.bfloat16 and q_half.is_contiguous() and q_half.numel() == q_out.numel()),
+          "rope_store: bad bfloat16 copy of the queries")
+    _need(rot == 0 or (cos_sin is not None and cos_sin.dtype == torch.float32 and cos_sin.is_contiguous()
+                       and tuple(cos_sin.shape[1:]) == (rot // 2, 2)), "rope_store: bad table of angles")
+    if store:
+        _need(k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.dtype == v_pages.dtype
+              and tuple(k_pages.shape[1:]) == (num_kv_heads, k_pages.shape[2], dk)
+              and tuple(v_pages.shape[1:]) == (num_kv_heads, k_pages.shape[2], dv), "rope_store: bad pages")
+        _need(block_table.dtype == torch.int32 and block_table.is_contiguous(), "rope_store: bad block table")
+    _check(lib().ms_rope_store(
+        _ptr(proj), proj.stride(0), _ptr(cos_sin if rot else None), int(rot), int(bool(interleaved)), cos_sin.shape[0] if rot else 0,
+        _ptr(positions), _ptr(slot_of_token), _ptr(block_table), block_table.shape[1] if store else 0, k_pages.shape[0] if store else 0,
+        k_pages.shape[2] if store else 0, _ptr(q_out), _ptr(q_half), _ptr(k_pages if store else None), _ptr(v_pages if store else None),
+        _code(k_pages) if store else F32, t, num_heads, num_kv_heads, dk, dv, int(store), _stream()), "rope_store")
+    return q_out
+
+
+def gdr_prepare(proj, x_off: int, b_off: int, a_off: int, conv_w, a_log, dt_bias, state, conv_off: int, cu_tokens, seq_of_token,
+                slot_of_token, qkv, bg, heads: int, groups: int, dk: int, dv: int, q_scale: float):
+    """What the gated delta rule's recurrence reads, from the step's input product: the short causal convolution (weights
+    conv_w float32 [C, taps], last column the current token's; the inputs before the step's first row come from the
+    request's state) and SiLU of the C = 2*groups*dk + heads*dv channels [q | k | v] at column x_off of proj; q and k heads
+    as unit vectors (x / sqrt(sum x^2 + 1e-6)), q times q_scale; beta = sigmoid(proj[:, b_off + h]); g = exp(-exp(a_log[h]) *
+    softplus(proj[:, a_off + h] + dt_bias[h])).  qkv float32 [T, C] and bg float32 [T, 2*heads] (beta | g) are written.
+    state float32 [slots, stride]: a slot's last taps - 1 inputs lie from conv_off on, [taps - 1, C], oldest first."""
+    t, c = qkv.shape
+    taps = conv_w.shape[1]
+    _need(proj.dtype == torch.float32 and proj.stride(1) == 1 and qkv.dtype == torch.float32 and qkv.is_contiguous()
+          and bg.dtype == torch.float32 and bg.is_contiguous() and tuple(bg.shape) == (t, 2 * heads)
+          and c == 2 * groups * dk + heads * dv, "gdr_prepare: bad layout")
+    _need(conv_w.dtype == torch.float32 and conv_w.is_contiguous() and conv_w.shape[0] == c, "gdr_prepare: bad convolution weights")
+    _need(all(v.dtype == torch.float32 and v.is_contiguous() and v.numel() == heads for v in (a_log, dt_bias)), "gdr_prepare: bad head constants")
+    _need(state.dtype == torch.float32 and state.is_contiguous() and state.dim() == 2
+          and state.shape[1] >= conv_off + (taps - 1) * c, "gdr_prepare: bad state")
+    _check(lib().ms_gdr_prepare(_ptr(proj), proj.stride(0), int(x_off), int(b_off), int(a_off), _ptr(conv_w), taps, _ptr(a_log), _ptr(dt_bias),
+                                _ptr(state), state.shape[1], int(conv_off), _ptr(cu_tokens), _ptr(seq_of_token), _ptr(slot_of_token),
+                                _ptr(qkv), _ptr(bg), t, heads, groups, dk, dv, float(q_scale), _stream()), "gdr_prepare")
+    return qkv, bg
+
+
+def gdr_conv_update(proj, x_off: int, taps: int, channels: int, state, conv_off: int, cu_tokens, state_slots, slot_of_token, seqs: int):
+    """After `gdr_prepare`: every sequence's last taps - 1 inputs (of its state's, then the step's) become its state's."""
+    _need(proj.dtype == torch.float32 and proj.stride(1) == 1 and state.dtype == torch.float32 and state.is_contiguous()
+          and state.dim() == 2 and state.shape[1] >= conv_off + (taps - 1) * channels, "gdr_conv_update: bad layout")
+    _check(lib().ms_gdr_conv_update(_ptr(proj), proj.stride(0), int(x_off), int(taps), _ptr(state), state.shape[1], int(conv_off),
+                                    _ptr(cu_tokens), _ptr(state_slots), _ptr(slot_of_token), int(seqs), int(channels), _stream()),
+           "gdr_conv_update")
+
+
+def gdr_scan(qkv, bg, state, cu_tokens, state_slots, slot_of_token, out, seqs: int, heads: int, groups: int, dk: int, dv: int,
+             narrow: bool = False):
+    """The recurrence S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q per sequence and value head (q/k head
+    h // (heads / groups)), over the rows of the step in order, from and to `state` (float32 [slots, stride], the matrices
+    [heads, dk, dv] at the start of a slot's row).  qkv, bg as `gdr_prepare` leaves them; out float32 [T, heads*dv].
+    `narrow`: blocks of 8 value columns instead of 32 (more blocks a sequence); same bits."""
+    t = qkv.shape[0]
+    _need(qkv.dtype == torch.float32 and qkv.is_contiguous() and qkv.shape[1] == 2 * groups * dk + heads * dv and bg.dtype == torch.float32
+          and bg.is_contiguous() and tuple(bg.shape) == (t, 2 * heads) and out.dtype == torch.float32 and out.is_contiguous()
+          and tuple(out.shape) == (t, heads * dv), "gdr_scan: bad layout")
+    _need(state.dtype == torch.float32 and state.is_contiguous() and state.dim() == 2 and state.shape[1] >= heads * dk * dv, "gdr_scan: bad state")
+    _need(cu_tokens.numel() >= seqs + 1 and state_slots.numel() >= seqs, "gdr_scan: bad sequence lists")
+    _check(lib().ms_gdr_scan(_ptr(qkv), _ptr(bg), _ptr(state), state.shape[1], _ptr(cu_tokens), _ptr(state_slots), _ptr(slot_of_token),
+                             _ptr(out), int(seqs), heads, groups, dk, dv, int(narrow), _stream()), "gdr_scan")
+    return out
+
+
 # ------------------------------------------------------------------------------------------------ routed feed-forward
 
 
@@ -1338,15 +1453,34 @@ def moe_route(logits, top: int, ids, weights, bias=None):
     return ids, weights
 
 
+def moe_route_scored(logits, top: int, ids, weights, correction=None, groups: int = 1, keep: int = 1, scale: float = 1.0):
+    """The choice by scores: s = sigmoid(logits) (float32 [T, E]); an expert is chosen by s + correction (float32 [E] or None),
+    among the experts of the `keep` best of `groups` equal groups of neighbours (a group's score: the sum of its two largest
+    choice scores; the lower index wins a tie); ids int32 [T, top] in descending order of the choice scores, weights float32
+    [T, top] = the chosen experts' s over their sum (+ 1e-20), times `scale`."""
+    t, e = logits.shape
+    _need(logits.dtype == torch.float32 and logits.is_contiguous() and ids.dtype == torch.int32 and ids.is_contiguous()
+          and weights.dtype == torch.float32 and weights.is_contiguous() and tuple(ids.shape) == (t, top) and tuple(weights.shape) == (t, top),
+          "moe_route_scored: bad arguments")
+    _need(correction is None or (correction.dtype == torch.float32 and correction.is_contiguous() and correction.numel() == e),
+          "moe_route_scored: bad correction")
+    _check(lib().ms_moe_route_scored(_ptr(logits), _ptr(correction), e, int(top), int(groups), int(keep), float(scale), _ptr(ids),
+                                     _ptr(weights), t, _stream()), "moe_route_scored")
+    return ids, weights
+
+
 def moe_gate_up_pairs(x, w_gate, w_up, ids, slot_of_token, h, activation: str):
-    """h[t*top + j, :] = act(w_gate[e] x_t) * (w_up[e] x_t) with e = ids[t, j].  x [T, d]; w_gate, w_up [E, ff, d];
+    """h[t*top + j, :] = act(w_gate[e] x_t) * (w_up[e] x_t) with e = ids[t, j] (`w_up` None, experts without a gate:
+    act(w_gate[e] x_t) alone).  x [T, d]; w_gate, w_up [E, ff, d];
     h [T*top, ff]; all of one dtype (float32 or bfloat16).  Rows with a negative slot get zeros."""
     t, d = x.shape
     experts, ff, _ = w_gate.shape
     top = ids.shape[1]
-    _need(x.is_contiguous() and w_gate.is_contiguous() and w_up.is_contiguous() and h.is_contiguous() and ids.is_contiguous()
-          and x.dtype == w_gate.dtype == w_up.dtype == h.dtype and tuple(w_up.shape) == (experts, ff, d) and w_gate.shape[2] == d
+    _need(x.is_contiguous() and w_gate.is_contiguous() and h.is_contiguous() and ids.is_contiguous()
+          and x.dtype == w_gate.dtype == h.dtype and w_gate.shape[2] == d
           and tuple(h.shape) == (t * top, ff) and ids.dtype == torch.int32 and ids.shape[0] == t, "moe_gate_up_pairs: bad arguments")
+    _need(w_up is None or (w_up.is_contiguous() and w_up.dtype == x.dtype and tuple(w_up.shape) == (experts, ff, d)),
+          "moe_gate_up_pairs: bad second matrix")
     step = max(1, 65535 // top)
     for t0 in range(0, t, step):
         n = min(step, t - t0)
@@ -1392,9 +1526,11 @@ def moe_grouped(x, w_gate, w_up, w_down, ids, weights, slot_of_token, scratch, h
     experts, ff, _ = w_gate.shape
     top = ids.shape[1]
     bf = torch.bfloat16
-    _need(x.dtype == bf and w_gate.dtype == bf and w_up.dtype == bf and w_down.dtype == bf and h.dtype == bf and x.is_contiguous()
-          and w_gate.is_contiguous() and w_up.is_contiguous() and w_down.is_contiguous() and h.is_contiguous(), "moe_grouped: bad operands")
-    _need(tuple(w_up.shape) == (experts, ff, d) and tuple(w_down.shape) == (experts, d, ff) and w_gate.shape[2] == d
+    _need(x.dtype == bf and w_gate.dtype == bf and w_down.dtype == bf and h.dtype == bf and x.is_contiguous()
+          and w_gate.is_contiguous() and w_down.is_contiguous() and h.is_contiguous(), "moe_grouped: bad operands")
+    _need(w_up is None or (w_up.dtype == bf and w_up.is_contiguous() and tuple(w_up.shape) == (experts, ff, d)),
+          "moe_grouped: bad second matrix")  # (None: experts without a gate, h = act(w_gate x))
+    _need(tuple(w_down.shape) == (experts, d, ff) and w_gate.shape[2] == d
           and tuple(h.shape) == (t * top, ff) and tuple(z.shape) == (t * top, d) and tuple(y.shape) == (t, d)
           and z.dtype == torch.float32 and y.dtype == torch.float32 and z.is_contiguous() and y.is_contiguous(), "moe_grouped: bad shapes")
     _need(ids.dtype == torch.int32 and ids.is_contiguous() and weights.dtype == torch.float32 and weights.is_contiguous()

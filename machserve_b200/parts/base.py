@@ -75,7 +75,16 @@ class FixedState:
     shape: Tuple[int, ...]
 
 
-CacheNeed = Union[PagedCache, FixedState, None]
+@dataclass(frozen=True)
+class CacheSet:
+    """What a mixer made of several mixers keeps: the needs of its members, in their order (each a `PagedCache`, a
+    `FixedState` or None).  The mixer is handed a tuple of bindings in the same order; the pages of a member join the group
+    of every other run with an equal need, a member's state lies in the request's state slot like any other."""
+
+    needs: Tuple[Union[PagedCache, FixedState, None], ...]
+
+
+CacheNeed = Union[PagedCache, FixedState, CacheSet, None]
 
 
 # --------------------------------------------------------------------- runtime
@@ -175,13 +184,26 @@ class DeltaPair:
     b: torch.Tensor
 
 
-def as_delta(pending, pairs: bool = False):
+@dataclass
+class ScaledDelta:
+    """A delta that is to be multiplied by a constant as it is added (a layer whose halves enter the stream with a
+    multiplier): the stream gets stream + scale * delta.  A norm that sets `accepts_scaled` does the product in its own
+    kernel, in float32; for every other part `as_delta` makes the scaled tensor."""
+
+    delta: torch.Tensor
+    scale: float
+
+
+def as_delta(pending, pairs: bool = False, scaled: bool = False):
     """What a norm adds to the residual before it normalises: a `RowStats` says that the add has been done; a
-    `DeltaPair` is summed (in float32) unless the caller takes pairs."""
+    `DeltaPair` is summed (in float32) unless the caller takes pairs; a `ScaledDelta` is multiplied out (in float32)
+    unless the caller takes it as it is."""
     if isinstance(pending, RowStats):
         return None
     if isinstance(pending, DeltaPair) and not pairs:
         return pending.a.float() + pending.b.float()
+    if isinstance(pending, ScaledDelta) and not scaled:
+        return pending.delta.float() * pending.scale
     return pending
 
 
@@ -306,6 +328,7 @@ class Norm(Part):
     """
 
     accepts_pairs = False  # True: `delta` may also be a `DeltaPair`, whose sum the norm adds
+    accepts_scaled = False  # True: `delta` may also be a `ScaledDelta`, which the norm multiplies as it adds
 
     def forward(self, residual, delta, out, rows=None):
         raise NotImplementedError
@@ -386,6 +409,7 @@ class Block:
 
     accepts_row_stats = False
     accepts_pairs = False  # True: `pending` may also be a `DeltaPair`
+    accepts_scaled = False  # True: `pending` may also be a `ScaledDelta`
     optional_feed_forward = False  # True: the block also arranges a layer that has no feed-forward
     kernel_files = ()  # what the block itself launches beyond its parts' kernels (see `Part.kernel_files`)
 

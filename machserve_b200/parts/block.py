@@ -1,7 +1,7 @@
 """Arrangements of a layer's parts around the residual stream."""
 from __future__ import annotations
 
-from .base import Block, DeltaPair, as_delta, register_block
+from .base import Block, DeltaPair, ScaledDelta, as_delta, register_block
 
 
 @register_block("prenorm")
@@ -20,31 +20,57 @@ class PreNormBlock(Block):
     same for the part after it, so that neither the norm nor the add needs a kernel of
     its own.  Each half of the block decides for itself; a part without the protocol is
     given normed rows and returns a delta, as ever.
+
+    block_params: `residual_scale` m (default 1): x += m * mixer(norm(x)); x += m * feed_forward(norm(x)).  The deltas are
+    handed on with their multiplier (`ScaledDelta`) and the norm that adds them multiplies, in float32; the few-row path,
+    whose products add into the stream themselves, is not taken then.  A layer without a feed-forward is
+    x += m * mixer(norm(x)) alone.
     """
 
     graph_safe = True
     accepts_row_stats = True
+    accepts_scaled = True
+    optional_feed_forward = True
     kernel_files = None  # (its parts' few-row path: not said)
+
+    def __init__(self, spec, mixer, feed_forward, mixer_norm, ff_norm):
+        super().__init__(spec, mixer, feed_forward, mixer_norm, ff_norm)
+        self.scale = float(spec.block_params.get("residual_scale", 1.0))
+        if (feed_forward is None) != (ff_norm is None):
+            raise ValueError("a pre-norm layer has a feed-forward and its norm, or neither")
+        if self.scale != 1.0 or feed_forward is None:
+            # the few-row path is the only thing the block launches beyond its parts' kernels
+            self.kernel_files = ()
 
     def bind(self, tensors, rt):
         super().bind(tensors, rt)
-        self.fuse_mixer = bool(self.mixer.fuse_norm(self.mixer_norm))
-        self.fuse_feed_forward = bool(self.feed_forward.fuse_norm(self.ff_norm))
+        plain = self.scale == 1.0
+        self.fuse_mixer = plain and bool(self.mixer.fuse_norm(self.mixer_norm))
+        self.fuse_feed_forward = plain and self.feed_forward is not None and bool(self.feed_forward.fuse_norm(self.ff_norm))
+
+    def _scaled(self, delta):
+        return delta if self.scale == 1.0 else ScaledDelta(delta, self.scale)
+
+    @staticmethod
+    def _for(norm, pending):
+        return as_delta(pending, scaled=norm.accepts_scaled)
 
     def forward(self, ctx, residual, pending, cache, owns_cache=True):
         rt = ctx.rt
         t, d = residual.shape
-        if self.fuse_mixer and t <= self.mixer.fused_rows:
+        if self.fuse_mixer and t <= self.mixer.fused_rows and not isinstance(pending, ScaledDelta):
             pending = self.mixer.forward_fused(ctx, residual, pending, self.mixer_norm, cache, owns_cache)
         else:
             xn = rt.workspace.get("block.normed", (t, d), rt.dtype)
-            self.mixer_norm.forward(residual, as_delta(pending), xn)
-            pending = self.mixer.forward(ctx, xn, cache, owns_cache)
+            self.mixer_norm.forward(residual, self._for(self.mixer_norm, pending), xn)
+            pending = self._scaled(self.mixer.forward(ctx, xn, cache, owns_cache))
+        if self.feed_forward is None:
+            return pending
         if self.fuse_feed_forward and t <= self.feed_forward.fused_rows:
             return self.feed_forward.forward_fused(ctx, residual, pending, self.ff_norm)
         xn = rt.workspace.get("block.normed", (t, d), rt.dtype)
-        self.ff_norm.forward(residual, as_delta(pending), xn)
-        return self.feed_forward.forward(ctx, xn)
+        self.ff_norm.forward(residual, self._for(self.ff_norm, pending), xn)
+        return self._scaled(self.feed_forward.forward(ctx, xn))
 
 
 @register_block("parallel")

@@ -17,6 +17,7 @@ class Embedding(TokenEmbedding):
     """
 
     graph_safe = True
+    kernel_files = ()
 
     def __init__(self, spec):
         super().__init__(spec)
@@ -77,7 +78,9 @@ class LMHead(Head):
     tensor may be absent and the embedding table stands in
     (crates/mach-model/src/loader.rs:1025-1033); if it is present it is used.
 
-    params: tensor, tied_to (name of the embedding tensor, or None), vocab_size, hidden_size.
+    With `softcap` c the logits become c * tanh(logits / c), in float32.
+
+    params: tensor, tied_to (name of the embedding tensor, or None), vocab_size, hidden_size, softcap (or None).
     """
 
     graph_safe = True
@@ -87,6 +90,7 @@ class LMHead(Head):
         super().__init__(spec)
         self.name, self.tied_to = spec["tensor"], spec.get("tied_to")
         self.vocab, self.hidden = int(spec["vocab_size"]), int(spec["hidden_size"])
+        self.softcap = float(spec["softcap"]) if spec.get("softcap") else None
 
     def tensors(self):
         out = [TensorDecl(self.name, (self.vocab, self.hidden), required=self.tied_to is None, random=self.tied_to is None)]
@@ -104,4 +108,5 @@ class LMHead(Head):
             self.weight = matrix(tensors[self.tied_to], rt)
 
     def forward(self, ctx, x, out):
-        return ops.linear(x, self.weight, None, out)
+        ops.linear(x, self.weight, None, out)
+        return ops.softcap(out, self.softcap) if self.softcap else out

@@ -13,7 +13,7 @@ import torch
 from ..config.spec import LayerSpec, ModelSpec
 from ..weights.loader import TensorDecl
 from .base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, STREAM_ENTRIES, Block, CacheNeed, DeltaPair, Part, Runtime,
-                   as_delta)
+                   ScaledDelta, as_delta)
 
 
 def build_block(layer: LayerSpec) -> Block:
@@ -128,8 +128,8 @@ class DecoderModel:
             if i in self.entries:
                 pending = self.entries[i].forward(ctx, residual, pending, first)
             if not block.accepts_row_stats:  # a block of another kind sees a delta or None, as every norm does
-                pending = as_delta(pending, pairs=block.accepts_pairs)
-            elif isinstance(pending, DeltaPair):
+                pending = as_delta(pending, pairs=block.accepts_pairs, scaled=block.accepts_scaled)
+            elif isinstance(pending, DeltaPair) or (isinstance(pending, ScaledDelta) and not block.accepts_scaled):
                 pending = as_delta(pending)
             pending = block.forward(ctx, residual, pending, caches[i], run.cache_of is None)
             if tap is not None:  # the delta a block hands on is part of the hidden rows after it
@@ -137,7 +137,8 @@ class DecoderModel:
                 tap(i, residual.clone() if delta is None else residual + delta[: residual.shape[0]].float())
         w = ctx.want_rows.shape[0]
         final = ws.get("model.final", (w, spec.hidden_size), rt.dtype)
-        self.final_norm.forward(residual, as_delta(pending, pairs=self.final_norm.accepts_pairs), final, rows=ctx.want_rows)
+        last = as_delta(pending, pairs=self.final_norm.accepts_pairs, scaled=self.final_norm.accepts_scaled)
+        self.final_norm.forward(residual, last, final, rows=ctx.want_rows)
         logits = ws.get("model.logits", (w, spec.vocab_size), torch.float32)
         return self.head.forward(ctx, final, logits)
 

@@ -3,7 +3,7 @@ from __future__ import annotations
 
 from .. import ops
 from ..weights.loader import TensorDecl
-from .base import DeltaPair, Norm, as_delta, register_norm, vector_f32
+from .base import DeltaPair, Norm, ScaledDelta, as_delta, register_norm, vector_f32
 
 
 @register_norm("rmsnorm")
@@ -17,6 +17,7 @@ class RMSNorm(Norm):
     graph_safe = True
     kernel_files = ('stream',)
     accepts_pairs = True  # a `DeltaPair` is summed and added by a kernel of its own (x + (a + b), float32)
+    accepts_scaled = True  # a `ScaledDelta` is multiplied by the same kernel as it is added (x + m * a, float32)
 
     def __init__(self, spec):
         super().__init__(spec)
@@ -32,6 +33,8 @@ class RMSNorm(Norm):
     def forward(self, residual, delta, out, rows=None):
         if isinstance(delta, DeltaPair):
             return ops.add_streams_rmsnorm(residual, delta.a, delta.b, None, None, self.weight, out, self.eps, rows)
+        if isinstance(delta, ScaledDelta):
+            return ops.add_streams_rmsnorm(residual, delta.delta, None, None, None, self.weight, out, self.eps, rows, delta.scale)
         return ops.add_rmsnorm(residual, as_delta(delta), self.weight, out, self.eps, rows)
 
     def fold_into(self, matrix):
