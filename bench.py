@@ -34,6 +34,11 @@ alone beside the like kernels of the dense decoder, each with its fraction of th
 `--only fozutar` (not part of the default run either) does the same for the Fozutar design (attention in chunks with a
 soft cap and a bias by distance, gated linear attention, dense and routed feed-forwards).
 
+`--only modadra` (not part of the default run either) times the Modadra design (windowed attention with a partial rotation,
+one more in the softmax's denominator and head gates beside a gated delta rule, their normed outputs averaged; experts
+without a gate behind a router of sigmoid scores with groups) beside the Fozutar design and the dense decoder at the same
+sizes, and its kernels alone beside the like kernels of those.
+
 This engine runs on one GPU: for --gpus > 1 it says so and exits with 2.
 
     python bench.py --kernel attention_prefill
@@ -891,6 +896,259 @@ def workload_fozutar(a, pk):
             "data": "random-init weights drawn on the device, seeded uniform random token ids", "peaks": pk["source"], "sizes": out}
 
 
+def modadra_config(raw, layers, window=1024):
+    """A Modadra configuration with the layer sizes of the Qwen2 shape `raw`: the same width, vocabulary, heads, key heads
+    and head size on the attention side (keys and values of the head size, half of every head rotated, a window of `window`
+    positions); beside it a gated delta rule with half as many value heads of twice the head size, a key head for every
+    two of them and a convolution of four taps; every layer's feed-forward routed (eight experts in four groups of which two
+    are kept, two experts a token, each half the shape's size: the same multiply-adds a token as a gated dense one of that
+    size has in two of its three matrices)."""
+    d, i, v, hq, hkv, hd = sizes(raw)
+    heads = max(1, hq // 2)
+    kv = heads // 2 if heads % 2 == 0 else heads
+    left = {"heads": hq, "kv_heads": hkv, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "rot": {"dims": hd // 2, "base": 10000.0},
+            "mask": {"size": window}}
+    right = {"heads": heads, "kv_heads": kv, "dim": hd, "vdim": 2 * hd, "conv": 4}
+    moe = {"kind": "moe", "expert": {"ff": i // 2 // 32 * 32}, "router": {"experts": 8, "top": 2, "scale": 1.5, "groups": {"count": 4, "keep": 2}}}
+    return {"architecture": "Modadra", "vocab": v, "width": d, "max_positions": 8192, "norm": {"eps": 1e-6}, "residual_mult": 0.5,
+            "logit_softcap": 30.0, "layers": [{"type": "parallel", "mixer": {"left": left, "right": right}, "mlp": moe} for _ in range(layers)]}
+
+
+def time_modadra_kernels(torch, ops, raw, pk):
+    """The Modadra design's kernels alone, each beside the like kernel of the closest designs at equal sizes where there is
+    one (inputs larger than the L2; a CUDA graph of a few launches between events)."""
+    d, inter, _, hq, hkv, hd = sizes(raw)
+    dev, bf = "cuda:0", torch.bfloat16
+    g = torch.Generator(device=dev).manual_seed(0)
+    rnd = lambda *shape, dt=torch.float32, scale=1.0: (torch.randn(*shape, device=dev, generator=g) * scale).to(dt)
+
+    def us(fn, reps=5):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(reps):
+                fn()
+        graph.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps * 1000
+
+    out = {}
+
+    def entry(name, t_new, t_like=None, nbytes=None, flops=None, like_bytes=None, like_flops=None, like="(no like kernel)"):
+        e = {"us": round(t_new, 1), "like": like}
+        if t_like is not None:
+            e["like_us"] = round(t_like, 1)
+        if nbytes:
+            e["hbm_frac"] = round(nbytes / t_new / 1e3 / pk["hbm_gbs"], 3)
+            if t_like is not None:
+                e["like_hbm_frac"] = round((like_bytes or nbytes) / t_like / 1e3 / pk["hbm_gbs"], 3)
+        if flops:
+            e["tensor_frac"] = round(flops / t_new / 1e6 / pk["bf16_tflops"], 4)
+            if t_like is not None:
+                e["like_tensor_frac"] = round((like_flops or flops) / t_like / 1e6 / pk["bf16_tflops"], 4)
+        out[name] = e
+
+    # the mean of the two mixers' normed outputs: 32,768 rows
+    rows = 32768
+    da, db, res = rnd(rows, d), rnd(rows, d), rnd(rows, d)
+    w = rnd(d)
+    o32, o16 = torch.empty(rows, d, device=dev), torch.empty(rows, d, dtype=bf, device=dev)
+    t_new = us(lambda: ops.norm_pair_mean(da, db, w, w, o32, 1e-6, 0.5))
+    t_like = us(lambda: ops.add_rmsnorm(res, da, w, o16, 1e-6))
+    entry("norm_pair_mean", t_new, t_like, rows * d * 12, like_bytes=rows * d * (4 + 4 + 4 + 2), like="add_rmsnorm (one delta)")
+    del da, db, res, o32, o16
+    # between the input product and the attention: 16,384 rows; the head gates after it
+    rows, page = 16384, PAGE
+    pos = (torch.arange(rows, dtype=torch.int32, device=dev) % 4096).contiguous()
+    slot = (torch.arange(rows, dtype=torch.int32, device=dev) // 4096).contiguous()
+    pages = rows // page
+    table = torch.arange(pages, dtype=torch.int32, device=dev).view(4, -1).contiguous()
+    proj = rnd(rows, (hq + 2 * hkv) * hd + hq)
+    kp, vp = torch.zeros(pages, hkv, page, hd, dtype=bf, device=dev), torch.zeros(pages, hkv, page, hd, dtype=bf, device=dev)
+    qo, qh = torch.empty(rows, hq * hd, device=dev), torch.empty(rows, hq * hd, dtype=bf, device=dev)
+    half = torch.zeros(4096, hd // 4, 2, device=dev)
+    t_new = us(lambda: ops.rope_store(proj, half, hd // 2, False, pos, slot, table, qo, kp, vp, hq, hkv, hd, hd, q_half=qh))
+    proj16, qo16 = rnd(rows, (hq + 2 * hkv) * hd, dt=bf), torch.empty(rows, hq * hd, dtype=bf, device=dev)
+    ang = torch.zeros(4096, hd // 2, 2, device=dev)
+    t_like = us(lambda: ops.rope_kv_store(proj16, None, pos, slot, table, ang, hd, False, qo16, kp, vp, hq, hkv, hd))
+    entry("rope_store", t_new, t_like, rows * ((hq + 2 * hkv) * hd * 4 + hq * hd * 6 + 2 * hkv * hd * 2),
+          like_bytes=rows * ((hq + 2 * hkv) * hd * 2 + hq * hd * 2 + 2 * hkv * hd * 2), like="rope_kv_store (bfloat16 in and out)")
+    gate = proj[:, (hq + 2 * hkv) * hd:]
+    t_new = us(lambda: ops.head_gate_mul(qh, gate, qh, hq, hd))
+    gu16 = rnd(rows, 2 * hq * hd, dt=bf)
+    t_like = us(lambda: ops.silu_mul(gu16, qo16))
+    entry("head_gate_mul", t_new, t_like, rows * hq * hd * 4, like_bytes=rows * hq * hd * 6, like="silu_mul")
+    del proj, proj16, qo, qo16, qh, kp, vp, gu16
+    # attention with the one more in the denominator under a window of 1,024: 64 decoding rows at 4,096 tokens and one prompt
+    # of 4,096 tokens, each on the kernel that the dense decoder uses, with and without the sink
+    from types import SimpleNamespace
+
+    from machserve_b200.parts.attention import decode_launch
+
+    window, ctx, b = 1024, 4096, 64
+    pages = b * ctx // page
+    table = torch.arange(pages, dtype=torch.int32, device=dev).view(b, -1).contiguous()
+    kp, vp = rnd(pages, hkv, page, hd, dt=bf), rnd(pages, hkv, page, hd, dt=bf)
+    sinks = torch.zeros(hq, device=dev)
+    q16 = rnd(b, hq * hd, dt=bf)
+    o = torch.empty(b, hq * hd, dtype=bf, device=dev)
+    posd = torch.full((b,), ctx - 1, dtype=torch.int32, device=dev)
+    slotd = torch.arange(b, dtype=torch.int32, device=dev)
+    if ops.attention_decode_supports(hd, hq // hkv):
+        sp, stg, wr, kpw, parts = decode_launch(SimpleNamespace(sm_count=ops.sm_count()), hd, ops.attention_decode_cluster_max_stages(hd), {},
+                                                b * hkv, -(-window // 64) + 1)
+        run = lambda sk: ops.attention_decode_cluster(q16, kp, vp, o, posd, slotd, table, hq, hkv, hd, window, 0.1, sp, stg, warps=wr,
+                                                      keys_per_warp=kpw, parts=1, sinks=sk)
+        t_new, t_like = us(lambda: run(sinks)), us(lambda: run(None))
+        entry("sink_window_attention_decode", t_new, t_like, b * window * hkv * 2 * hd * 2, like="the same kernel without the sink")
+    n = ctx
+    posp = torch.arange(n, dtype=torch.int32, device=dev)
+    slotp = torch.zeros(n, dtype=torch.int32, device=dev)
+    if ops.attention_prefill_tc_supports(hd, page):
+        qp16, op = rnd(n, hq * hd, dt=bf), torch.empty(n, hq * hd, dtype=bf, device=dev)
+        t0 = torch.arange(0, n, 128, dtype=torch.int32, device=dev)
+        tn = torch.full_like(t0, 128)
+        tiles = t0.numel()
+        splits_p, alone, run_tiles = ops.attention_prefill_tc_plan(tiles, hq, hkv, hd, window + 128, tiles * 9)
+        words = ops.attention_prefill_tc_scratch_words(tiles, hq, hd, splits_p)
+        scr = torch.zeros(max(words, 1), dtype=torch.float32, device=dev) if words else None
+        counters = torch.zeros(tiles * hq, dtype=torch.int32, device=dev) if words else None
+        run = lambda sk: ops.attention_prefill_tc(qp16, kp, vp, op, t0, tn, tiles, posp, slotp, table, hq, hkv, hd, window, 0.1, splits_p,
+                                                  scr, counters, alone=alone, run_tiles=run_tiles, sinks=sk)
+        t_new, t_like = us(lambda: run(sinks), reps=2), us(lambda: run(None), reps=2)
+        flops = 4 * sum(min(p + 1, window) for p in range(n)) * hq * hd
+        entry("sink_window_attention_prefill", t_new, t_like, flops=flops, like="the same tcgen05 kernel without the sink")
+        del qp16, op
+    del kp, vp, q16, o
+    # the recurrence: what it reads from the input product (4,096 rows), 64 sequences of one token, and one sequence of 4,096
+    heads = max(1, hq // 2)
+    kv = heads // 2 if heads % 2 == 0 else heads
+    dk, dv, taps = hd, 2 * hd, 4
+    kw, vw = kv * dk, heads * dv
+    ch = 2 * kw + vw
+    width = ch + vw + 2 * heads
+    conv_off = heads * dk * dv
+    state = torch.zeros(b, conv_off + (taps - 1) * ch, device=dev)
+    proj = rnd(n, width, scale=0.3)
+    conv_w, a_log, dt_bias = rnd(ch, taps, scale=0.5), rnd(heads, scale=0.3), rnd(heads, scale=0.3)
+    qkv, bg = torch.empty(n, ch, device=dev), torch.empty(n, 2 * heads, device=dev)
+    cup = torch.tensor([0, n], dtype=torch.int32, device=dev)
+    zero = torch.zeros(n, dtype=torch.int32, device=dev)
+    t_new = us(lambda: (ops.gdr_prepare(proj, 0, ch + vw, ch + vw + heads, conv_w, a_log, dt_bias, state, conv_off, cup, zero, zero, qkv, bg,
+                                        heads, kv, dk, dv, dk ** -0.5),
+                        ops.gdr_conv_update(proj, 0, taps, ch, state, conv_off, cup, zero[:1], zero, 1)))
+    gkw, gvw = heads * dk, heads * dv  # (the gated linear attention of the same heads: what it computes between product and scan)
+    gproj = rnd(n, 2 * gkw + 2 * gvw + 16, scale=0.1)
+    w2 = rnd(gkw, 16, dt=bf)
+    dec = torch.empty(n, gkw, device=dev)
+    t_like = us(lambda: ops.gla_decay(gproj[:, 2 * gkw + 2 * gvw:], w2, None, 16.0, dec))
+    entry("gdr_prepare_and_conv_update", t_new, t_like, n * (ch * 4 * 2 + 2 * heads * 4 * 2), like_bytes=n * (16 * 4 + gkw * 4),
+          like="gla_decay (what the gated linear attention computes before its scan)")
+    og = torch.empty(n, vw, device=dev)
+    cu1 = torch.arange(b + 1, dtype=torch.int32, device=dev)
+    t_new = us(lambda: ops.gdr_scan(qkv[:b], bg[:b], state, cu1, slotd, slotd, og[:b], b, heads, kv, dk, dv))
+    gstate = torch.zeros(b, heads, dk, dv, device=dev)
+    dec.uniform_(0.9, 1.0)
+    t_like = us(lambda: ops.gla_scan(gproj[:b], 0, gkw, 2 * gkw, dec[:b], 0.1, gstate, cu1, slotd, slotd, og[:b], b, heads, dk, dv))
+    entry("gdr_scan_decode", t_new, t_like, 2 * b * heads * dk * dv * 4, like="gla_scan (decode)")
+    t_new = us(lambda: ops.gdr_scan(qkv, bg, state, cup, zero[:1], zero, og, 1, heads, kv, dk, dv, narrow=True), reps=2)
+    t_like = us(lambda: ops.gla_scan(gproj, 0, gkw, 2 * gkw, dec, 0.1, gstate, cup, zero[:1], zero, og, 1, heads, dk, dv, narrow=True), reps=2)
+    # (CUDA-core multiply-adds, the scan is sequential: three products of the state a token here, two there)
+    entry("gdr_scan_prefill", t_new, t_like, flops=n * heads * dk * dv * 6, like_flops=n * heads * dk * dv * 4, like="gla_scan (one prompt)")
+    y = torch.empty(n, vw, dtype=bf, device=dev)
+    normw = rnd(dv)
+    t_new = us(lambda: ops.gla_output(og, proj[:, ch:ch + vw], normw, 1e-6, y, heads, dv))
+    entry("gdr_output (gla_output)", t_new, nbytes=n * vw * (4 + 4 + 2), like="the same kernel")
+    del state, proj, qkv, bg, og, gproj, dec, gstate, y
+    # the soft cap on the logits: 64 rows of the vocabulary
+    v = raw["vocab_size"]
+    lg = rnd(b, v)
+    t_new = us(lambda: ops.softcap(lg, 30.0))
+    entry("softcap", t_new, nbytes=b * v * 8)
+    del lg
+    # the router and the experts without a gate: eight experts, two a token; 8 decoding rows and 4,096 rows of a prompt, beside
+    # the gated experts of the same sizes under the softmax router
+    experts, top, ff = 8, 2, inter // 2 // 32 * 32
+    wg, wu, wd = rnd(experts, ff, d, dt=bf, scale=0.02), rnd(experts, ff, d, dt=bf, scale=0.02), rnd(experts, d, ff, dt=bf, scale=0.02)
+    corr = rnd(experts, scale=0.1)
+    for t, name in ((8, "decode"), (4096, "prefill")):
+        x = rnd(t, d, dt=bf)
+        logits = rnd(t, experts)
+        ids, weights = torch.empty(t, top, dtype=torch.int32, device=dev), torch.empty(t, top, device=dev)
+        if t > 16:
+            big = rnd(1 << 20, experts)
+            bi, bw = torch.empty(1 << 20, top, dtype=torch.int32, device=dev), torch.empty(1 << 20, top, device=dev)
+            t_new = us(lambda: ops.moe_route_scored(big, top, bi, bw, corr, 4, 2, 1.5))
+            t_like = us(lambda: ops.moe_route(big, top, bi, bw))
+            entry("moe_route_scored", t_new, t_like, (1 << 20) * (experts * 4 + top * 8), like="moe_route (softmax over the chosen)")
+            del big, bi, bw
+        ops.moe_route_scored(logits, top, ids, weights, corr, 4, 2, 1.5)
+        hbuf = torch.empty(t * top, ff, dtype=bf, device=dev)
+        yb = torch.empty(t, d, device=dev)
+        slots = torch.zeros(t, dtype=torch.int32, device=dev)
+        if t <= 16:
+            t_new = us(lambda: (ops.moe_route_scored(logits, top, ids, weights, corr, 4, 2, 1.5),
+                                ops.moe_gate_up_pairs(x, wu, None, ids, slots, hbuf, "gelu"), ops.moe_down_pairs(hbuf, wd, ids, weights, slots, yb)))
+            t_like = us(lambda: (ops.moe_route(logits, top, ids, weights), ops.moe_gate_up_pairs(x, wg, wu, ids, slots, hbuf, "silu"),
+                                 ops.moe_down_pairs(hbuf, wd, ids, weights, slots, yb)))
+            touched = min(experts, t * top)
+            entry("ungated_experts_" + name, t_new, t_like, nbytes=touched * 2 * ff * d * 2, like_bytes=touched * 3 * ff * d * 2,
+                  like="gated experts of the same sizes (pair by pair)")
+        else:
+            scratch = torch.empty(ops.moe_grouped_scratch_ints(t * top, experts), dtype=torch.int32, device=dev)
+            z = torch.empty(t * top, d, device=dev)
+            t_new = us(lambda: (ops.moe_route_scored(logits, top, ids, weights, corr, 4, 2, 1.5),
+                                ops.moe_grouped(x, wu, None, wd, ids, weights, slots, scratch, hbuf, z, yb, "gelu")), reps=2)
+            t_like = us(lambda: (ops.moe_route(logits, top, ids, weights),
+                                 ops.moe_grouped(x, wg, wu, wd, ids, weights, slots, scratch, hbuf, z, yb, "silu")), reps=2)
+            entry("ungated_experts_" + name, t_new, t_like, flops=4 * t * top * ff * d, like_flops=6 * t * top * ff * d,
+                  like="gated experts of the same sizes (sorted tiles)")
+    return out
+
+
+def workload_modadra(a, pk):
+    """The Modadra design at the layer sizes of the Qwen2.5 shapes, beside the Fozutar design (the closest one: attention,
+    a recurrent mixer and routed experts too) and the dense decoder at the same sizes: decode at the headline batch and
+    context, one prompt of `--prefill` tokens, and the new kernels alone."""
+    import torch
+
+    from machserve_b200 import ops
+
+    out = {}
+    shapes = sorted(SHAPES) if a.modadra_shapes == "all" else [x.strip() for x in a.modadra_shapes.split(",") if x.strip()]
+    for shape in shapes:
+        raw = SHAPES[shape]
+        layers = min(raw["num_hidden_layers"], a.layers or 12)  # (layers of like sizes: twelve tell what all tell)
+        res = {"layers": layers}
+        steps = max(10, a.steps // 2)
+        for which in ("modadra", "fozutar", "dense"):
+            kw = {}
+            if which != "dense":
+                kw = dict(config=(modadra_config if which == "modadra" else fozutar_config)(raw, layers), vocab=raw["vocab_size"])
+            b = DecodeBench(a, raw, layers, "bf16", a.batch, a.context + 4 * (steps + a.warmup) + a.batch + 64, **kw)
+            times, launches = b.time_decode(a.batch, a.context, steps, a.warmup, blocks=3, sampled=False)
+            pms = b.time_prefill(a.prefill, 2, reps=3)
+            res[which] = {"decode_ms_per_step": round(times[len(times) // 2], 4), "decode_tokens_per_s": round(a.batch * 1000.0 / times[len(times) // 2], 1),
+                          "launches_per_step": launches // steps, "prefill_ms": round(pms, 3), "prefill_tokens_per_s": round(a.prefill * 1000.0 / pms, 1)}
+            b.runner.check_device_status()
+            b.release_all()
+            del b
+            free_device_memory()
+        if not a.no_points:
+            res["kernels"] = time_modadra_kernels(torch, ops, raw, pk)
+        free_device_memory()
+        out[shape] = res
+    return {"batch": a.batch, "context": a.context, "prefill_tokens": a.prefill, "dtype": "bf16",
+            "data": "random-init weights drawn on the device, seeded uniform random token ids", "peaks": pk["source"], "sizes": out}
+
+
 def workload_serving(a, pk):
     """Qwen2.5-1.5B sizes: 64 requests, prompts of 128 to 2,048 tokens (seeded), 256 new tokens each, through `Engine`
     with its default budget of prompt tokens per step.  All requests arrive at time zero.  Three loads of other prompt
@@ -1074,10 +1332,12 @@ def main() -> int:
     ap.add_argument("--only", default="headline,fp32,serving_1p5b,mixed_7b",
                     help="which parts to run: headline, fp32, serving_1p5b, mixed_7b (comma separated); venarax, which is not "
                          "among the defaults, times the Venarax design beside the dense decoder at equal layer sizes; fozutar, "
-                         "likewise not among the defaults, does the same for the Fozutar design")
+                         "likewise not among the defaults, does the same for the Fozutar design; modadra, not among the defaults "
+                         "either, times the Modadra design beside the Fozutar design and the dense decoder")
     ap.add_argument("--no-points", action="store_true", help="skip the further batch sizes and the prefill (venarax: the kernels alone)")
     ap.add_argument("--venarax-shapes", default="all", help="the shapes of the venarax workload (comma separated), or all")
     ap.add_argument("--fozutar-shapes", default="all", help="the shapes of the fozutar workload (comma separated), or all")
+    ap.add_argument("--modadra-shapes", default="all", help="the shapes of the modadra workload (comma separated), or all")
     ap.add_argument("--profile", default=None, choices=["decode", "prefill", "mixed"],
                     help="which timed region is bracketed by cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     ap.add_argument("--kernel", default=None, choices=["attention_prefill", "gemm"],
@@ -1195,6 +1455,8 @@ def main() -> int:
         line["venarax"] = workload_venarax(a, pk)
     if "fozutar" in only:
         line["fozutar"] = workload_fozutar(a, pk)
+    if "modadra" in only:
+        line["modadra"] = workload_modadra(a, pk)
     print(json.dumps(line))
     return 0
 

@@ -381,7 +381,7 @@ def test_convolution_unit_vectors_gates_and_the_delta_rule(heads, groups, dk, dv
     for s, slot in enumerate(slots):  # what a slot holds behind the matrices: the sequence's last taps - 1 inputs, oldest first
         rows = p64[starts[s] : starts[s + 1], off["x"] : off["x"] + off["c"]]
         held = np.concatenate([np.zeros((taps - 1, off["c"])), rows])[len(rows) :]
-        assert np.array_equal(state[slot, conv_off : conv_off + (taps - 1) * off["c"]].cpu().numpy().reshape(taps - 1, -1), held.astype(np.float32))
+        assert np.array_equal(state[slot, conv_off : conv_off + (taps - 1) * off["c"]].cpu().numpy().reshape(taps - 1, off["c"]), held.astype(np.float32))
         assert float(state[slot, conv_off + (taps - 1) * off["c"] :].min()) == 0.0
 
 
