@@ -127,11 +127,46 @@ __global__ void head_gate_mul_kernel(const T* x, const float* __restrict__ gate,
   out[i] = ms_from_float<T>(ms_to_float(x[i]) / (1.f + expf(-g)));
 }
 
+// The same with 16 bytes a thread (dv a multiple of the 16 / sizeof(T) elements that a thread takes, so that they lie in
+// one head; x and out 16-byte aligned): an element's arithmetic is that of the kernel above.
+template <typename T>
+__global__ void head_gate_mul_vec_kernel(const T* x, const float* __restrict__ gate, int ldg, T* out, int heads, int dv, size_t groups) {
+  constexpr int E = 16 / sizeof(T);
+  ms_pdl_trigger();
+  ms_pdl_wait();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= groups) return;
+  const int per_row = heads * dv / E;
+  const size_t r = i / per_row;
+  const int h = (int)(i - r * per_row) * E / dv;
+  const float s = 1.f + expf(-gate[r * ldg + h]);
+  union {
+    uint4 u;
+    T e[E];
+  } v;
+  v.u = reinterpret_cast<const uint4*>(x)[i];
+#pragma unroll
+  for (int k = 0; k < E; ++k) v.e[k] = ms_from_float<T>(ms_to_float(v.e[k]) / s);
+  reinterpret_cast<uint4*>(out)[i] = v.u;
+}
+
 MS_API int ms_head_gate_mul(const void* x, const float* gate, int ldg, void* out, int dtype, int rows, int heads, int dv,
                             cudaStream_t stream) {
   if (rows == 0) return 0;
   MS_REQUIRE(rows > 0 && heads > 0 && dv > 0 && ldg >= heads, "head_gate_mul: bad sizes rows=%d heads=%d dv=%d", rows, heads, dv);
   const size_t total = (size_t)rows * heads * dv;
+  const int per = dtype == MS_F32 ? 4 : 8;
+  if ((dtype == MS_F32 || dtype == MS_BF16) && dv % per == 0 && (((uintptr_t)x | (uintptr_t)out) & 15) == 0) {
+    const size_t groups = total / per;
+    const unsigned vblocks = (unsigned)((groups + 255) / 256);
+    if (dtype == MS_F32)
+      MS_LAUNCH_RESULT("head_gate_mul", ms_launch(head_gate_mul_vec_kernel<float>, dim3(vblocks), dim3(256), 0, stream, 1, true,
+                                                  (const float*)x, gate, ldg, (float*)out, heads, dv, groups));
+    else
+      MS_LAUNCH_RESULT("head_gate_mul", ms_launch(head_gate_mul_vec_kernel<__nv_bfloat16>, dim3(vblocks), dim3(256), 0, stream, 1, true,
+                                                  (const __nv_bfloat16*)x, gate, ldg, (__nv_bfloat16*)out, heads, dv, groups));
+    return 0;
+  }
   const unsigned blocks = (unsigned)((total + 255) / 256);
   if (dtype == MS_F32)
     MS_LAUNCH_RESULT("head_gate_mul", ms_launch(head_gate_mul_kernel<float>, dim3(blocks), dim3(256), 0, stream, 1, true, (const float*)x, gate,

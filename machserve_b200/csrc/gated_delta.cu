@@ -14,7 +14,8 @@
 // gdr_conv_update:  a thread a (sequence, channel): the state's last taps - 1 inputs after the step's rows.
 // gdr_scan:         a block owns COLS value columns of one head of one sequence and goes through the sequence's rows of the step
 //                   in order, from the state the step found to the state it leaves.  Eight lanes share a column: lane (c, g)
-//                   holds KPT consecutive key rows of column c in registers.  With a = k . S_old[:, c], b = q . S_old[:, c] and
+//                   holds KPT key rows of column c in registers, W (4, or 2) neighbours out of every 8 W, so that the eight
+//                   lanes of a column read a staged q or k with loads that lie side by side.  With a = k . S_old[:, c], b = q . S_old[:, c] and
 //                   qk = q . k (three sums over the eight lanes, by exchange within the warp, every lane the same bits):
 //                     u = beta (v - g a),  o = g b + qk u,  S[:, c] <- g S[:, c] + k u.
 //                   q, k, v, beta and g of 16 tokens at a time are staged in shared memory, the next batch on its way while
@@ -102,12 +103,13 @@ __device__ __forceinline__ void gdr_cp_async4(float* smem, const float* gmem) {
 }
 
 template <int KPT, int COLS>
-__global__ void __launch_bounds__(COLS * GDR_LPC)
+__global__ void __launch_bounds__(COLS * GDR_LPC + (COLS == 8 ? 32 : 0), (COLS == 32 && KPT <= 16) ? 2 : 1)
 gdr_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ bg, float* __restrict__ state, long long stride,
                 const int* __restrict__ cu_tokens, const int* __restrict__ state_slots, const int* __restrict__ slot_of_token,
                 float* __restrict__ o, int heads, int groups, int dk, int dv, int vec) {
   constexpr int KP = KPT * GDR_LPC;       // key rows, padded
   constexpr int ROW = 2 * KP + COLS + 4;  // floats of one token in a stage: q | k | v | beta, g, -, -
+  constexpr int W = KPT % 4 == 0 ? 4 : 2;  // key rows that a lane reads with one load (KPT is a multiple of 2)
   extern __shared__ __align__(16) float gdr_smem[];
   float* stage0 = gdr_smem;                       // [2][GDR_TB][ROW]
   float* obuf = gdr_smem + 2 * GDR_TB * ROW;      // [GDR_TB][COLS]
@@ -117,9 +119,13 @@ gdr_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ bg, flo
   const int row0 = cu_tokens[seq], rows = cu_tokens[seq + 1] - row0;
   if (rows <= 0 || slot_of_token[row0] < 0) return;  // a sequence of no rows, or rows of no request
   const int slot = state_slots[seq];
-  const int grp = threadIdx.x % GDR_LPC, c = threadIdx.x / GDR_LPC;  // (the lanes of a column are neighbours in a warp)
+  // blocks of few columns (long portions) have one warp more, which does nothing but request the batches: the lanes that
+  // walk the chain of tokens spend no instruction on it
+  constexpr bool FEEDER = COLS == 8;
+  const bool feeds = FEEDER && threadIdx.x >= COLS * GDR_LPC;
+  const int grp = threadIdx.x % GDR_LPC, c = feeds ? 0 : threadIdx.x / GDR_LPC;  // (the lanes of a column are neighbours in a warp)
   const int col = c0 + c;
-  const bool live = col < dv;
+  const bool live = !feeds && col < dv;
   const int qh = h / (heads / groups);
   const int C = 2 * groups * dk + heads * dv;
   // padding of the key rows: q = k = 0 for good, in both stages
@@ -129,8 +135,9 @@ gdr_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ bg, flo
     t[r] = 0.f;
     t[KP + r] = 0.f;
   }
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31, warp = FEEDER ? 0 : threadIdx.x >> 5, nwarps = FEEDER ? 1 : blockDim.x >> 5;
   auto request = [&](int t0, int st) {
+    if (FEEDER && !feeds) return;
     const int nt = min(GDR_TB, rows - t0);
     float* base = stage0 + (size_t)st * GDR_TB * ROW;
     for (int tb = warp; tb < nt; tb += nwarps) {
@@ -167,9 +174,64 @@ gdr_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ bg, flo
   float s[KPT];
 #pragma unroll
   for (int i = 0; i < KPT; ++i) {
-    const int r = grp * KPT + i;
+    const int r = (i / W) * (GDR_LPC * W) + grp * W + i % W;
     s[i] = (live && r < dk) ? st[(size_t)r * dv + col] : 0.f;
   }
+  // one token's inputs in registers: this lane's key rows of q and k, the column's v, the head's beta and g, and q . k
+  struct Tok {
+    float q[KPT], k[KPT], v, beta, g, qk;
+  };
+  auto fetch = [&](const float* t, Tok& x) {
+    x.v = t[2 * KP + c];
+    x.beta = t[2 * KP + COLS];
+    x.g = t[2 * KP + COLS + 1];
+#pragma unroll
+    for (int i = 0; i < KPT; i += W) {
+      const int at = (i / W) * (GDR_LPC * W) + grp * W;
+      if constexpr (W == 4) {
+        const float4 q4 = *reinterpret_cast<const float4*>(t + at);
+        const float4 k4 = *reinterpret_cast<const float4*>(t + KP + at);
+        x.q[i] = q4.x; x.q[i + 1] = q4.y; x.q[i + 2] = q4.z; x.q[i + 3] = q4.w;
+        x.k[i] = k4.x; x.k[i + 1] = k4.y; x.k[i + 2] = k4.z; x.k[i + 3] = k4.w;
+      } else {
+        const float2 q2 = *reinterpret_cast<const float2*>(t + at);
+        const float2 k2 = *reinterpret_cast<const float2*>(t + KP + at);
+        x.q[i] = q2.x; x.q[i + 1] = q2.y;
+        x.k[i] = k2.x; x.k[i + 1] = k2.y;
+      }
+    }
+    // q . k does not read the state: it is summed while the token before is still being worked on
+    float p[W];
+#pragma unroll
+    for (int j = 0; j < W; ++j) p[j] = 0.f;
+#pragma unroll
+    for (int i = 0; i < KPT; ++i) p[i % W] = fmaf(x.q[i], x.k[i], p[i % W]);
+    float qk = W == 4 ? (p[0] + p[1]) + (p[2] + p[W - 1]) : p[0] + p[W - 1];
+#pragma unroll
+    for (int off = 1; off < GDR_LPC; off <<= 1) qk += __shfl_xor_sync(0xffffffffu, qk, off);
+    x.qk = qk;
+  };
+  auto work = [&](const Tok& x, int tb) {
+    float pa[W], pb[W];
+#pragma unroll
+    for (int j = 0; j < W; ++j) pa[j] = pb[j] = 0.f;
+#pragma unroll
+    for (int i = 0; i < KPT; ++i) {  // W sums side by side, so that a lane's chain of additions is KPT / W long
+      pa[i % W] = fmaf(x.k[i], s[i], pa[i % W]);
+      pb[i % W] = fmaf(x.q[i], s[i], pb[i % W]);
+    }
+    float a = W == 4 ? (pa[0] + pa[1]) + (pa[2] + pa[W - 1]) : pa[0] + pa[W - 1];
+    float b = W == 4 ? (pb[0] + pb[1]) + (pb[2] + pb[W - 1]) : pb[0] + pb[W - 1];
+#pragma unroll
+    for (int off = 1; off < GDR_LPC; off <<= 1) {  // both lanes of a pair add the same two numbers: the same bits in every lane
+      a += __shfl_xor_sync(0xffffffffu, a, off);
+      b += __shfl_xor_sync(0xffffffffu, b, off);
+    }
+    const float u = x.beta * (x.v - x.g * a);
+#pragma unroll
+    for (int i = 0; i < KPT; ++i) s[i] = fmaf(x.g, s[i], x.k[i] * u);
+    if (grp == 0) obuf[tb * COLS + c] = fmaf(x.g, b, x.qk * u);
+  };
   int stg = 0;
   for (int t0 = 0; t0 < rows; t0 += GDR_TB, stg ^= 1) {
     const int nt = min(GDR_TB, rows - t0);
@@ -178,42 +240,29 @@ gdr_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ bg, flo
     if (t0 + GDR_TB < rows) request(t0 + GDR_TB, stg ^ 1);
     asm volatile("cp.async.commit_group;\n" ::);
     const float* base = stage0 + (size_t)stg * GDR_TB * ROW;
-    for (int tb = 0; tb < nt; ++tb) {
-      const float* t = base + (size_t)tb * ROW;
-      const float v = t[2 * KP + c], beta = t[2 * KP + COLS], g = t[2 * KP + COLS + 1];
-      float qr[KPT], kr[KPT];
-      if constexpr (KPT % 4 == 0) {
-#pragma unroll
-        for (int i = 0; i < KPT; i += 4) {
-          const float4 q4 = *reinterpret_cast<const float4*>(t + grp * KPT + i);
-          const float4 k4 = *reinterpret_cast<const float4*>(t + KP + grp * KPT + i);
-          qr[i] = q4.x; qr[i + 1] = q4.y; qr[i + 2] = q4.z; qr[i + 3] = q4.w;
-          kr[i] = k4.x; kr[i + 1] = k4.y; kr[i + 2] = k4.z; kr[i + 3] = k4.w;
-        }
-      } else {
-#pragma unroll
-        for (int i = 0; i < KPT; ++i) {
-          qr[i] = t[grp * KPT + i];
-          kr[i] = t[KP + grp * KPT + i];
+    if (feeds) {
+      // (nothing between the two barriers)
+    } else if constexpr (COLS == 8) {
+      // blocks of few columns are for long portions: the next token's inputs are on their way while this one's chain
+      // (a -> u -> S) runs
+      Tok even, odd;
+      fetch(base, even);
+      for (int tb = 0; tb < nt; tb += 2) {
+        if (tb + 1 < nt) fetch(base + (size_t)(tb + 1) * ROW, odd);
+        work(even, tb);
+        if (tb + 1 < nt) {
+          if (tb + 2 < nt) fetch(base + (size_t)(tb + 2) * ROW, even);
+          work(odd, tb + 1);
         }
       }
-      float a = 0.f, b = 0.f, qk = 0.f;
-#pragma unroll
-      for (int i = 0; i < KPT; ++i) {
-        a = fmaf(kr[i], s[i], a);
-        b = fmaf(qr[i], s[i], b);
-        qk = fmaf(qr[i], kr[i], qk);
+    } else {
+      // blocks of many columns are for steps of single tokens, where the state's way from and to memory is what counts:
+      // fewer registers, more blocks on a multiprocessor
+      for (int tb = 0; tb < nt; ++tb) {
+        Tok x;
+        fetch(base + (size_t)tb * ROW, x);
+        work(x, tb);
       }
-#pragma unroll
-      for (int off = 1; off < GDR_LPC; off <<= 1) {  // both lanes of a pair add the same two numbers: the same bits in every lane
-        a += __shfl_xor_sync(0xffffffffu, a, off);
-        b += __shfl_xor_sync(0xffffffffu, b, off);
-        qk += __shfl_xor_sync(0xffffffffu, qk, off);
-      }
-      const float u = beta * (v - g * a);
-#pragma unroll
-      for (int i = 0; i < KPT; ++i) s[i] = fmaf(g, s[i], kr[i] * u);
-      if (grp == 0) obuf[tb * COLS + c] = fmaf(g, b, qk * u);
     }
     __syncthreads();
     for (int e = threadIdx.x; e < nt * COLS; e += blockDim.x) {
@@ -223,7 +272,7 @@ gdr_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ bg, flo
   }
 #pragma unroll
   for (int i = 0; i < KPT; ++i) {
-    const int r = grp * KPT + i;
+    const int r = (i / W) * (GDR_LPC * W) + grp * W + i % W;
     if (live && r < dk) st[(size_t)r * dv + col] = s[i];
   }
 }
@@ -236,7 +285,7 @@ static int gdr_scan_launch(cudaStream_t stream, int seqs, const float* qkv, cons
   const int vec = dk % 4 == 0 && dv % 4 == 0 && C % 4 == 0 && (uintptr_t)qkv % 16 == 0;
   constexpr int KP = KPT * GDR_LPC;
   const size_t smem = (size_t)(2 * GDR_TB * (2 * KP + COLS + 4) + GDR_TB * COLS) * sizeof(float);
-  const dim3 grid((dv + COLS - 1) / COLS, heads, seqs), block(COLS * GDR_LPC);
+  const dim3 grid((dv + COLS - 1) / COLS, heads, seqs), block(COLS * GDR_LPC + (COLS == 8 ? 32 : 0));
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(gdr_scan_kernel<KPT, COLS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

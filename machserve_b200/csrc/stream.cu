@@ -184,7 +184,10 @@ MS_API int ms_add_streams_rmsnorm(float* residual, const void* a, int a_dtype, c
 
 // ------------------------------------------------------------------------------------------------------------------
 
-// One block a row; a and b float32 [rows, d]; the row's two sums of squares are taken side by side.
+// One block a row; a and b float32 [rows, d]; the row's two sums of squares are taken side by side.  VEC: d is a multiple of
+// 4, every pointer 16-byte aligned and d <= ST_THREADS * NP_KEEP * 4: both rows stay in registers between the two passes.
+#define NP_KEEP 4
+template <bool VEC>
 __global__ void __launch_bounds__(ST_THREADS)
 norm_pair_mean_kernel(const float* __restrict__ a, const float* __restrict__ b, const float* __restrict__ wa, const float* __restrict__ wb,
                       float* __restrict__ out, int d, float eps, float m) {
@@ -193,23 +196,63 @@ norm_pair_mean_kernel(const float* __restrict__ a, const float* __restrict__ b, 
   ms_pdl_wait();
   const size_t base = (size_t)blockIdx.x * d;
   float sa = 0.f, sb = 0.f;
-  for (int c = threadIdx.x; c < d; c += blockDim.x) {
-    const float x = a[base + c], y = b[base + c];
-    sa += x * x;
-    sb += y * y;
+  if constexpr (VEC) {
+    float4 x[NP_KEEP], y[NP_KEEP];
+    const int ngroups = d / 4;
+    const float4* a4 = reinterpret_cast<const float4*>(a + base);
+    const float4* b4 = reinterpret_cast<const float4*>(b + base);
+#pragma unroll
+    for (int i = 0; i < NP_KEEP; ++i) {
+      const int g = threadIdx.x + i * ST_THREADS;
+      if (g < ngroups) {
+        x[i] = a4[g];
+        y[i] = b4[g];
+        sa += x[i].x * x[i].x + x[i].y * x[i].y + x[i].z * x[i].z + x[i].w * x[i].w;
+        sb += y[i].x * y[i].x + y[i].y * y[i].y + y[i].z * y[i].z + y[i].w * y[i].w;
+      }
+    }
+    sa = ms_block_sum(sa, scratch_a);
+    sb = ms_block_sum(sb, scratch_b);
+    const float ia = rsqrtf(sa / (float)d + eps), ib = rsqrtf(sb / (float)d + eps);
+    float4* o4 = reinterpret_cast<float4*>(out + base);
+#pragma unroll
+    for (int i = 0; i < NP_KEEP; ++i) {
+      const int g = threadIdx.x + i * ST_THREADS;
+      if (g < ngroups) {
+        const float4 p = reinterpret_cast<const float4*>(wa)[g], q = reinterpret_cast<const float4*>(wb)[g];
+        float4 r;
+        r.x = m * (x[i].x * ia * p.x + y[i].x * ib * q.x);
+        r.y = m * (x[i].y * ia * p.y + y[i].y * ib * q.y);
+        r.z = m * (x[i].z * ia * p.z + y[i].z * ib * q.z);
+        r.w = m * (x[i].w * ia * p.w + y[i].w * ib * q.w);
+        o4[g] = r;
+      }
+    }
+  } else {
+    for (int c = threadIdx.x; c < d; c += blockDim.x) {
+      const float x = a[base + c], y = b[base + c];
+      sa += x * x;
+      sb += y * y;
+    }
+    sa = ms_block_sum(sa, scratch_a);
+    sb = ms_block_sum(sb, scratch_b);
+    const float ia = rsqrtf(sa / (float)d + eps), ib = rsqrtf(sb / (float)d + eps);
+    for (int c = threadIdx.x; c < d; c += blockDim.x) out[base + c] = m * (a[base + c] * ia * wa[c] + b[base + c] * ib * wb[c]);
   }
-  sa = ms_block_sum(sa, scratch_a);
-  sb = ms_block_sum(sb, scratch_b);
-  const float ia = rsqrtf(sa / (float)d + eps), ib = rsqrtf(sb / (float)d + eps);
-  for (int c = threadIdx.x; c < d; c += blockDim.x) out[base + c] = m * (a[base + c] * ia * wa[c] + b[base + c] * ib * wb[c]);
 }
 
 MS_API int ms_norm_pair_mean(const float* a, const float* b, const float* wa, const float* wb, float* out, int rows, int d, float eps,
                              float m, cudaStream_t stream) {
   if (rows == 0) return 0;
   MS_REQUIRE(rows > 0 && d > 0, "norm_pair_mean: bad sizes rows=%d d=%d", rows, d);
-  MS_LAUNCH_RESULT("norm_pair_mean", ms_launch(norm_pair_mean_kernel, dim3(rows), dim3(ST_THREADS), 0, stream, 1, true, a, b, wa, wb, out, d,
-                                               eps, m));
+  const bool vec = d % 4 == 0 && d <= ST_THREADS * NP_KEEP * 4 &&
+                   (((uintptr_t)a | (uintptr_t)b | (uintptr_t)wa | (uintptr_t)wb | (uintptr_t)out) & 15) == 0;
+  if (vec)
+    MS_LAUNCH_RESULT("norm_pair_mean", ms_launch(norm_pair_mean_kernel<true>, dim3(rows), dim3(ST_THREADS), 0, stream, 1, true, a, b, wa, wb,
+                                                 out, d, eps, m));
+  else
+    MS_LAUNCH_RESULT("norm_pair_mean", ms_launch(norm_pair_mean_kernel<false>, dim3(rows), dim3(ST_THREADS), 0, stream, 1, true, a, b, wa, wb,
+                                                 out, d, eps, m));
   return 0;
 }
 

@@ -158,7 +158,9 @@ CLOSE_CALL = 0.01  # a margin of a router's choice below this can fall either wa
 def plain_logits_and_close_calls(model_dir, tokens, bf16_weights: bool = False, tol: float = 0.02):
     """(logits [T, vocab], unsure [T] bool).  `unsure[t]` says that the plain model itself cannot vouch for row t under
     bfloat16 rounding: some router chose an expert or a group by less than CLOSE_CALL at token t, or the row's logits move by
-    more than `tol` (times their largest) when nothing but the layers' normed inputs are rounded to bfloat16.  A recurrent
+    more than `tol` (times their largest) when what a bfloat16 engine hands on in 16 bits (the layers' normed inputs, kept keys
+    and values, the rows that the output projections read) is rounded to bfloat16 and all else stays as it is (or the normed
+    inputs alone: two draws of the same noise).  A recurrent
     layer hands a wrong choice on to the rows after it, so every row after a close call of such a model is unsure too for as
     long as the state remembers: the callers compare long sequences of those cases in float32."""
     import torch
@@ -171,6 +173,8 @@ def plain_logits_and_close_calls(model_dir, tokens, bf16_weights: bool = False, 
     unsure = np.zeros(len(tokens), dtype=bool)
     for m in margins:
         unsure |= m < CLOSE_CALL
-    rounded = forward(cfg, w, tokens, None, None, lambda h: torch.from_numpy(h.astype(np.float32)).to(torch.bfloat16).to(torch.float64).numpy())
-    unsure |= np.abs(rounded - logits).max(-1) > tol * max(1.0, float(np.abs(logits).max()))
+    r16 = lambda h: torch.from_numpy(h.astype(np.float32)).to(torch.bfloat16).to(torch.float64).numpy()
+    for inner in (None, r16):  # two draws of the rounding: the normed inputs alone, and every place named above
+        rounded = forward(cfg, w, tokens, None, None, r16, inner)
+        unsure |= np.abs(rounded - logits).max(-1) > tol * max(1.0, float(np.abs(logits).max()))
     return logits, unsure

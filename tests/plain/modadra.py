@@ -74,7 +74,7 @@ def softmax_plus_one(s, visible):
     return e / (np.exp(-m) + e.sum(-1, keepdims=True))
 
 
-def windowed_attention(h, w, p, cfg):
+def windowed_attention(h, w, p, cfg, rnd=None):
     """Grouped heads, key and value widths of their own, rotation of a part of every head, a sliding window, the softmax
     with one added to its denominator, a gate per head from the mixer's input, the output projection."""
     t = h.shape[0]
@@ -84,6 +84,8 @@ def windowed_attention(h, w, p, cfg):
     q = rotate_half_partial((h @ w[p + "q"].T).reshape(t, H, dk), pos, rot.get("dims", 0), rot.get("base", 1.0))
     k = rotate_half_partial((h @ w[p + "k"].T).reshape(t, G, dk), pos, rot.get("dims", 0), rot.get("base", 1.0))
     v = (h @ w[p + "v"].T).reshape(t, G, dv)
+    rnd = rnd or (lambda a: a)  # (a rounding of what is kept for later tokens and of what the output projection reads)
+    k, v = rnd(k), rnd(v)
     gate = sigmoid(h @ w[p + "g"].T)  # [T, H]
     vis = window_mask(t, (cfg.get("mask") or {}).get("size"))
     out = np.zeros((t, H, dv))
@@ -91,7 +93,7 @@ def windowed_attention(h, w, p, cfg):
         g = head // (H // G)
         prob = softmax_plus_one(q[:, head] @ k[:, g].T * cfg["scale"], vis)
         out[:, head] = (prob @ v[:, g]) * gate[:, head : head + 1]
-    return out.reshape(t, H * dv) @ w[p + "o"].T
+    return rnd(out.reshape(t, H * dv)) @ w[p + "o"].T
 
 
 # ------------------------------------------------------------------------------------------ the recurrent half
@@ -127,7 +129,7 @@ def delta_rule(q, k, v, beta, g, state=None):
     return o, s
 
 
-def gated_delta(h, w, p, cfg, eps):
+def gated_delta(h, w, p, cfg, eps, rnd=None):
     t = h.shape[0]
     H, G, dk, dv = cfg["heads"], cfg["kv_heads"], cfg["dim"], cfg["vdim"]
     q = silu(short_conv(h @ w[p + "q"].T, w[p + "q.conv"])).reshape(t, G, dk)
@@ -142,13 +144,14 @@ def gated_delta(h, w, p, cfg, eps):
         g = head // (H // G)
         o[:, head], _ = delta_rule(q[:, g], k[:, g], v[:, head], beta[:, head], decay[:, head])
     o = unit_rms(o, eps) * w[p + "norm"]
-    return (o.reshape(t, H * dv) * silu(h @ w[p + "g"].T)) @ w[p + "o"].T
+    y = o.reshape(t, H * dv) * silu(h @ w[p + "g"].T)
+    return (y if rnd is None else rnd(y)) @ w[p + "o"].T
 
 
-def two_mixers(h, w, p, cfg, eps):
+def two_mixers(h, w, p, cfg, eps, rnd=None):
     """Both halves read h; each output is normed over the width with a weight of its own; half their sum."""
-    left = windowed_attention(h, w, p + "left.", cfg["left"])
-    right = gated_delta(h, w, p + "right.", cfg["right"], eps)
+    left = windowed_attention(h, w, p + "left.", cfg["left"], rnd)
+    right = gated_delta(h, w, p + "right.", cfg["right"], eps, rnd)
     return 0.5 * (rms_norm(left, w[p + "left.out"], eps) + rms_norm(right, w[p + "right.out"], eps))
 
 
@@ -186,30 +189,32 @@ def route(h, w, p, router, margins=None):
     return ids, chosen / (chosen.sum(-1, keepdims=True) + 1e-20) * router.get("scale", 1.0)
 
 
-def expert(x, w, q):
-    return gelu_erf(x @ w[q + "up"].T) @ w[q + "down"].T
+def expert(x, w, q, rnd=None):
+    mid = gelu_erf(x @ w[q + "up"].T)
+    return (mid if rnd is None else rnd(mid)) @ w[q + "down"].T
 
 
-def routed_mlp(h, w, p, cfg, margins=None):
+def routed_mlp(h, w, p, cfg, margins=None, rnd=None):
     ids, weights = route(h, w, p, cfg["router"], margins)
     out = np.zeros_like(h)
     for t in range(h.shape[0]):
         for e, a in zip(ids[t], weights[t]):
-            out[t] += a * expert(h[t], w, f"{p}e{int(e)}.")
+            out[t] += a * expert(h[t], w, f"{p}e{int(e)}.", rnd)
     return out
 
 
 # ------------------------------------------------------------------------------------------ the model
 
 
-def layer(x, w, i, spec, eps, mult, margins=None, round_h=None):
+def layer(x, w, i, spec, eps, mult, margins=None, round_h=None, round_inner=None):
     """x <- x + m * mixer(norm1(x)); then, if the layer has a feed-forward, x <- x + m * ff(norm2(x)).  `round_h`, a
-    function, is applied to the normed rows: what an engine does that hands them on in fewer bits."""
+    function, is applied to the normed rows, and `round_inner` to keys and values and to the rows that output projections
+    read: what an engine does that hands them on in fewer bits."""
     p = f"l{i}."
     rnd = round_h or (lambda a: a)
-    x = x + mult * two_mixers(rnd(rms_norm(x, w[p + "norm1"], eps)), w, p + "mix.", spec["mixer"], eps)
+    x = x + mult * two_mixers(rnd(rms_norm(x, w[p + "norm1"], eps)), w, p + "mix.", spec["mixer"], eps, round_inner)
     if spec.get("mlp") is not None:
-        x = x + mult * routed_mlp(rnd(rms_norm(x, w[p + "norm2"], eps)), w, p + "mlp.", spec["mlp"], margins)
+        x = x + mult * routed_mlp(rnd(rms_norm(x, w[p + "norm2"], eps)), w, p + "mlp.", spec["mlp"], margins, round_inner)
     return x
 
 
@@ -217,14 +222,14 @@ def soft_cap(z, cap):
     return cap * np.tanh(z / cap)
 
 
-def forward(config, w, tokens, taps=None, margins=None, round_h=None):
+def forward(config, w, tokens, taps=None, margins=None, round_h=None, round_inner=None):
     """Logits [T, vocab] of a whole sequence; `taps`, a list, receives the stream after every layer; `margins`, a list,
     receives the router's margins [T] of every routed feed-forward (see `route`)."""
     w = {k: np.asarray(v, dtype=np.float64) if np.asarray(v).dtype.kind == "f" else np.asarray(v) for k, v in w.items()}
     eps = config["norm"]["eps"]
     x = w["embed"][np.asarray(tokens, dtype=np.int64)]
     for i, spec in enumerate(config["layers"]):
-        x = layer(x, w, i, spec, eps, config.get("residual_mult", 1.0), margins, round_h)
+        x = layer(x, w, i, spec, eps, config.get("residual_mult", 1.0), margins, round_h, round_inner)
         if taps is not None:
             taps.append(x.copy())
     z = rms_norm(x, w["final.norm"], eps) @ w["head"].T
