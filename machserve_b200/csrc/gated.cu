@@ -124,30 +124,47 @@ __global__ void head_gate_mul_kernel(const T* x, const float* __restrict__ gate,
   const size_t r = i / n;
   const int h = (int)(i - r * n) / dv;
   const float g = gate[r * ldg + h];
-  out[i] = ms_from_float<T>(ms_to_float(x[i]) / (1.f + expf(-g)));
+  out[i] = ms_from_float<T>(ms_to_float(x[i]) * (1.f / (1.f + expf(-g))));
 }
 
 // The same with 16 bytes a thread (dv a multiple of the 16 / sizeof(T) elements that a thread takes, so that they lie in
 // one head; x and out 16-byte aligned): an element's arithmetic is that of the kernel above.
+#define HG_ROWS 4  // rows a thread takes: their loads are all requested before the first is used
 template <typename T>
-__global__ void head_gate_mul_vec_kernel(const T* x, const float* __restrict__ gate, int ldg, T* out, int heads, int dv, size_t groups) {
+__global__ void __launch_bounds__(256)
+head_gate_mul_vec_kernel(const T* x, const float* __restrict__ gate, int ldg, T* out, int rows, int dv, int per_row) {
   constexpr int E = 16 / sizeof(T);
   ms_pdl_trigger();
   ms_pdl_wait();
-  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= groups) return;
-  const int per_row = heads * dv / E;
-  const size_t r = i / per_row;
-  const int h = (int)(i - r * per_row) * E / dv;
-  const float s = 1.f + expf(-gate[r * ldg + h]);
-  union {
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;  // (threads are laid out by rows: no division finds the row)
+  if (j >= per_row) return;
+  const size_t r0 = (size_t)blockIdx.y * (blockDim.y * HG_ROWS) + threadIdx.y;
+  union V {
     uint4 u;
     T e[E];
-  } v;
-  v.u = reinterpret_cast<const uint4*>(x)[i];
+  };
+  uint4 raw[HG_ROWS];
+  float g[HG_ROWS];
 #pragma unroll
-  for (int k = 0; k < E; ++k) v.e[k] = ms_from_float<T>(ms_to_float(v.e[k]) / s);
-  reinterpret_cast<uint4*>(out)[i] = v.u;
+  for (int k = 0; k < HG_ROWS; ++k) {
+    const size_t r = r0 + (size_t)k * blockDim.y;
+    if (r < (size_t)rows) {
+      raw[k] = (reinterpret_cast<const uint4*>(x) + r * per_row)[j];
+      g[k] = gate[r * ldg + j * E / dv];
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < HG_ROWS; ++k) {
+    const size_t r = r0 + (size_t)k * blockDim.y;
+    if (r < (size_t)rows) {
+      const float s = 1.f / (1.f + expf(-g[k]));  // one division a head and thread, a product an element
+      V v;
+      v.u = raw[k];
+#pragma unroll
+      for (int i = 0; i < E; ++i) v.e[i] = ms_from_float<T>(ms_to_float(v.e[i]) * s);
+      (reinterpret_cast<uint4*>(out) + r * per_row)[j] = v.u;
+    }
+  }
 }
 
 MS_API int ms_head_gate_mul(const void* x, const float* gate, int ldg, void* out, int dtype, int rows, int heads, int dv,
@@ -156,15 +173,18 @@ MS_API int ms_head_gate_mul(const void* x, const float* gate, int ldg, void* out
   MS_REQUIRE(rows > 0 && heads > 0 && dv > 0 && ldg >= heads, "head_gate_mul: bad sizes rows=%d heads=%d dv=%d", rows, heads, dv);
   const size_t total = (size_t)rows * heads * dv;
   const int per = dtype == MS_F32 ? 4 : 8;
-  if ((dtype == MS_F32 || dtype == MS_BF16) && dv % per == 0 && (((uintptr_t)x | (uintptr_t)out) & 15) == 0) {
-    const size_t groups = total / per;
-    const unsigned vblocks = (unsigned)((groups + 255) / 256);
+  if ((dtype == MS_F32 || dtype == MS_BF16) && dv % per == 0 && (((uintptr_t)x | (uintptr_t)out) & 15) == 0 && rows <= 65535) {
+    const int per_row = heads * dv / per;
+    int tx = 32;
+    while (tx < 256 && tx < per_row) tx *= 2;
+    const int per_block = 256 / tx * HG_ROWS;
+    const dim3 threads(tx, 256 / tx), grid((per_row + tx - 1) / tx, (rows + per_block - 1) / per_block);
     if (dtype == MS_F32)
-      MS_LAUNCH_RESULT("head_gate_mul", ms_launch(head_gate_mul_vec_kernel<float>, dim3(vblocks), dim3(256), 0, stream, 1, true,
-                                                  (const float*)x, gate, ldg, (float*)out, heads, dv, groups));
+      MS_LAUNCH_RESULT("head_gate_mul", ms_launch(head_gate_mul_vec_kernel<float>, grid, threads, 0, stream, 1, true, (const float*)x, gate,
+                                                  ldg, (float*)out, rows, dv, per_row));
     else
-      MS_LAUNCH_RESULT("head_gate_mul", ms_launch(head_gate_mul_vec_kernel<__nv_bfloat16>, dim3(vblocks), dim3(256), 0, stream, 1, true,
-                                                  (const __nv_bfloat16*)x, gate, ldg, (__nv_bfloat16*)out, heads, dv, groups));
+      MS_LAUNCH_RESULT("head_gate_mul", ms_launch(head_gate_mul_vec_kernel<__nv_bfloat16>, grid, threads, 0, stream, 1, true,
+                                                  (const __nv_bfloat16*)x, gate, ldg, (__nv_bfloat16*)out, rows, dv, per_row));
     return 0;
   }
   const unsigned blocks = (unsigned)((total + 255) / 256);
