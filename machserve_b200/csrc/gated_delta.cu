@@ -177,11 +177,11 @@ gdr_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ bg, flo
     const int r = (i / W) * (GDR_LPC * W) + grp * W + i % W;
     s[i] = (live && r < dk) ? st[(size_t)r * dv + col] : 0.f;
   }
-  // one token's inputs in registers: this lane's key rows of q and k, the column's v, the head's beta and g, and q . k
+  // one token's inputs in registers: this lane's key rows of q and k, the column's v, the head's beta and g
   struct Tok {
-    float q[KPT], k[KPT], v, beta, g, qk;
+    float q[KPT], k[KPT], v, beta, g;
   };
-  auto fetch = [&](const float* t, Tok& x) {
+  auto fetch = [&](const float* t, Tok& x) {  // loads and nothing that waits for them: a warp issues in order
     x.v = t[2 * KP + c];
     x.beta = t[2 * KP + COLS];
     x.g = t[2 * KP + COLS + 1];
@@ -200,37 +200,34 @@ gdr_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ bg, flo
         x.k[i] = k2.x; x.k[i + 1] = k2.y;
       }
     }
-    // q . k does not read the state: it is summed while the token before is still being worked on
-    float p[W];
-#pragma unroll
-    for (int j = 0; j < W; ++j) p[j] = 0.f;
-#pragma unroll
-    for (int i = 0; i < KPT; ++i) p[i % W] = fmaf(x.q[i], x.k[i], p[i % W]);
-    float qk = W == 4 ? (p[0] + p[1]) + (p[2] + p[W - 1]) : p[0] + p[W - 1];
-#pragma unroll
-    for (int off = 1; off < GDR_LPC; off <<= 1) qk += __shfl_xor_sync(0xffffffffu, qk, off);
-    x.qk = qk;
   };
   auto work = [&](const Tok& x, int tb) {
-    float pa[W], pb[W];
+    float pa[W], pb[W], pq[W];
 #pragma unroll
-    for (int j = 0; j < W; ++j) pa[j] = pb[j] = 0.f;
+    for (int j = 0; j < W; ++j) pa[j] = pb[j] = pq[j] = 0.f;
+#pragma unroll
+    for (int i = 0; i < KPT; ++i) pa[i % W] = fmaf(x.k[i], s[i], pa[i % W]);  // (the sum that the state's next value waits for)
 #pragma unroll
     for (int i = 0; i < KPT; ++i) {  // W sums side by side, so that a lane's chain of additions is KPT / W long
-      pa[i % W] = fmaf(x.k[i], s[i], pa[i % W]);
       pb[i % W] = fmaf(x.q[i], s[i], pb[i % W]);
+      pq[i % W] = fmaf(x.q[i], x.k[i], pq[i % W]);
     }
     float a = W == 4 ? (pa[0] + pa[1]) + (pa[2] + pa[W - 1]) : pa[0] + pa[W - 1];
     float b = W == 4 ? (pb[0] + pb[1]) + (pb[2] + pb[W - 1]) : pb[0] + pb[W - 1];
+    float qk = W == 4 ? (pq[0] + pq[1]) + (pq[2] + pq[W - 1]) : pq[0] + pq[W - 1];
 #pragma unroll
     for (int off = 1; off < GDR_LPC; off <<= 1) {  // both lanes of a pair add the same two numbers: the same bits in every lane
-      a += __shfl_xor_sync(0xffffffffu, a, off);
-      b += __shfl_xor_sync(0xffffffffu, b, off);
+      const float a2 = __shfl_xor_sync(0xffffffffu, a, off);  // three exchanges under way at once, one wait a stage
+      const float b2 = __shfl_xor_sync(0xffffffffu, b, off);
+      const float q2 = __shfl_xor_sync(0xffffffffu, qk, off);
+      a += a2;
+      b += b2;
+      qk += q2;
     }
     const float u = x.beta * (x.v - x.g * a);
 #pragma unroll
     for (int i = 0; i < KPT; ++i) s[i] = fmaf(x.g, s[i], x.k[i] * u);
-    if (grp == 0) obuf[tb * COLS + c] = fmaf(x.g, b, x.qk * u);
+    if (grp == 0) obuf[tb * COLS + c] = fmaf(x.g, b, qk * u);
   };
   int stg = 0;
   for (int t0 = 0; t0 < rows; t0 += GDR_TB, stg ^= 1) {
