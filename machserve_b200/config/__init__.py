@@ -13,3 +13,4 @@ from .qwen2 import Qwen2Config  # noqa: F401
 from .venarax import VenaraxConfig  # noqa: F401
 from .fozutar import FozutarConfig  # noqa: F401
 from .modadra import ModadraConfig  # noqa: F401
+from .varolix import VarolixConfig  # noqa: F401

@@ -245,7 +245,7 @@ MS_API int ms_gla_scan(const float* proj, int ld, int q_off, int k_off, int v_of
 
 template <typename TO>
 __global__ void __launch_bounds__(128)
-gla_output_kernel(const float* __restrict__ o, const float* __restrict__ gate, int ldg, const float* __restrict__ w, float eps,
+gla_output_kernel(const float* __restrict__ o, int ldo, const float* __restrict__ gate, int ldg, const float* __restrict__ w, float eps,
                   TO* __restrict__ out, int heads, int dv, int items) {
   ms_pdl_trigger();
   ms_pdl_wait();
@@ -253,7 +253,7 @@ gla_output_kernel(const float* __restrict__ o, const float* __restrict__ gate, i
   const int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (item >= items) return;
   const int t = item / heads, h = item - t * heads;
-  const float* x = o + ((size_t)t * heads + h) * dv;
+  const float* x = o + (size_t)t * ldo + (size_t)h * dv;
   float ss = 0.f;
   for (int d = lane; d < dv; d += 32) ss += x[d] * x[d];
   ss = ms_warp_sum(ss);
@@ -269,18 +269,18 @@ gla_output_kernel(const float* __restrict__ o, const float* __restrict__ gate, i
   }
 }
 
-// o float32 [T, heads*dv]; gate float32 rows with stride ldg (the gate's columns begin at the pointer), or null; w float32 [dv].
-MS_API int ms_gla_output(const float* o, const float* gate, int ldg, const float* w, float eps, void* out, int out_dtype, int tokens,
+// o float32 rows of heads*dv with stride ldo; gate float32 rows with stride ldg (the gate's columns begin at the pointer), or null; w float32 [dv].
+MS_API int ms_gla_output(const float* o, int ldo, const float* gate, int ldg, const float* w, float eps, void* out, int out_dtype, int tokens,
                          int heads, int dv, cudaStream_t stream) {
   if (tokens == 0) return 0;
-  MS_REQUIRE(tokens > 0 && heads > 0 && dv > 0 && (gate == nullptr || ldg >= heads * dv), "gla_output: bad sizes");
+  MS_REQUIRE(tokens > 0 && heads > 0 && dv > 0 && ldo >= heads * dv && (gate == nullptr || ldg >= heads * dv), "gla_output: bad sizes");
   const int items = tokens * heads;
   const dim3 grid((items + 3) / 4), block(128);
   if (out_dtype == MS_F32)
-    MS_LAUNCH_RESULT("gla_output", ms_launch(gla_output_kernel<float>, grid, block, 0, stream, 1, true, o, gate, ldg, w, eps, (float*)out, heads,
+    MS_LAUNCH_RESULT("gla_output", ms_launch(gla_output_kernel<float>, grid, block, 0, stream, 1, true, o, ldo, gate, ldg, w, eps, (float*)out, heads,
                                              dv, items));
   else if (out_dtype == MS_BF16)
-    MS_LAUNCH_RESULT("gla_output", ms_launch(gla_output_kernel<__nv_bfloat16>, grid, block, 0, stream, 1, true, o, gate, ldg, w, eps,
+    MS_LAUNCH_RESULT("gla_output", ms_launch(gla_output_kernel<__nv_bfloat16>, grid, block, 0, stream, 1, true, o, ldo, gate, ldg, w, eps,
                                              (__nv_bfloat16*)out, heads, dv, items));
   else
     MS_REQUIRE(false, "gla_output: unknown out dtype %d", out_dtype);

@@ -5,13 +5,14 @@
 //   v_off of the product), or, v_off < 0, the keys as they were projected, before their norm.
 // proj is float32 [T, ld] = [q (hq*dk) | k (hkv*dk) | v], to which `bias` (float32, the same columns, or null) is added first;
 // q_out float32 [T, hq*dk] and, optionally, a bfloat16 copy.
+// With coef != 0 the normed query at position p is multiplied by 1 + coef * ln(floor((p + 1) / every) + 1).
 // One warp a head; the sums are float32 and their order depends on dk alone.  norm = 0 leaves q and k as they are.
 #include "launch.cuh"
 
 template <typename TC>
 __global__ void __launch_bounds__(128)
 head_norm_store_kernel(const float* __restrict__ proj, int ld, const float* __restrict__ bias, const float* __restrict__ wq,
-                       const float* __restrict__ wk, float eps,
+                       const float* __restrict__ wk, float eps, float coef, int every,
                        int norm, const int* __restrict__ positions, const int* __restrict__ slots, const int* __restrict__ block_table,
                        int max_pages, int num_pages, int page_size, float* __restrict__ q_out, __nv_bfloat16* __restrict__ q_half,
                        TC* __restrict__ k_pages, TC* __restrict__ v_pages, int hq, int hkv, int dk, int dv, int v_off, int store) {
@@ -22,6 +23,7 @@ head_norm_store_kernel(const float* __restrict__ proj, int ld, const float* __re
   const float* row = proj + (size_t)t * ld;
   const int slot = slots[t];
   int page = -1, off = 0;
+  const float temp = (coef != 0.f && slot >= 0) ? 1.f + coef * logf((float)((positions[t] + 1) / every + 1)) : 1.f;
   if (store && slot >= 0) {
     const int p = positions[t];
     page = block_table[(size_t)slot * max_pages + p / page_size];
@@ -41,7 +43,7 @@ head_norm_store_kernel(const float* __restrict__ proj, int ld, const float* __re
     const float* w = is_q ? wq : wk;
     if (is_q) {
       for (int d = lane; d < dk; d += 32) {
-        const float v = x(d) * inv * (w ? w[d] : 1.f);
+        const float v = x(d) * inv * (w ? w[d] : 1.f) * temp;
         q_out[((size_t)t * hq + h) * dk + d] = v;
         if (q_half) q_half[((size_t)t * hq + h) * dk + d] = __float2bfloat16_rn(v);
       }
@@ -60,24 +62,24 @@ head_norm_store_kernel(const float* __restrict__ proj, int ld, const float* __re
   }
 }
 
-MS_API int ms_head_norm_store(const float* proj, int ld, const float* bias, const float* wq, const float* wk, float eps, int norm,
-                              const int* positions,
+MS_API int ms_head_norm_store(const float* proj, int ld, const float* bias, const float* wq, const float* wk, float eps, float coef,
+                              int every, int norm, const int* positions,
                               const int* slots, const int* block_table, int max_pages, int num_pages, int page_size, float* q_out,
                               void* q_half, void* k_pages, void* v_pages, int cache_dtype, int tokens, int hq, int hkv, int dk, int dv,
                               int v_off, int store, cudaStream_t stream) {
   if (tokens == 0) return 0;
-  MS_REQUIRE(tokens > 0 && hq > 0 && hkv > 0 && dk > 0 && dv > 0, "head_norm_store: bad sizes");
+  MS_REQUIRE(tokens > 0 && hq > 0 && hkv > 0 && dk > 0 && dv > 0 && (coef == 0.f || every > 0), "head_norm_store: bad sizes");
   MS_REQUIRE(v_off >= 0 || dv == dk, "head_norm_store: values that are the keys have the keys' width (%d, not %d)", dk, dv);
   MS_REQUIRE(ld >= (store ? hq + hkv : hq) * dk && (!store || v_off < 0 || ld >= v_off + hkv * dv),
              "head_norm_store: the product's rows are too short (%d)", ld);
   MS_REQUIRE(!store || (max_pages > 0 && num_pages > 0 && page_size > 0 && k_pages && v_pages), "head_norm_store: bad cache");
   if (cache_dtype == MS_F32)
     MS_LAUNCH_RESULT("head_norm_store", ms_launch(head_norm_store_kernel<float>, dim3(tokens), dim3(128), 0, stream, 1, true, proj, ld, bias,
-                                                  wq, wk, eps, norm, positions, slots, block_table, max_pages, num_pages, page_size, q_out,
+                                                  wq, wk, eps, coef, every, norm, positions, slots, block_table, max_pages, num_pages, page_size, q_out,
                                                   (__nv_bfloat16*)q_half, (float*)k_pages, (float*)v_pages, hq, hkv, dk, dv, v_off, store));
   else if (cache_dtype == MS_BF16)
     MS_LAUNCH_RESULT("head_norm_store", ms_launch(head_norm_store_kernel<__nv_bfloat16>, dim3(tokens), dim3(128), 0, stream, 1, true, proj,
-                                                  ld, bias, wq, wk, eps, norm, positions, slots, block_table, max_pages, num_pages, page_size,
+                                                  ld, bias, wq, wk, eps, coef, every, norm, positions, slots, block_table, max_pages, num_pages, page_size,
                                                   q_out, (__nv_bfloat16*)q_half, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, hq, hkv,
                                                   dk, dv, v_off, store));
   else

@@ -9,23 +9,28 @@
 //   q_wide[t, h, r:r+dr] = turn(q[t, h, dn:dn+dr], p)        (float32; columns 0:r are filled by the product of the
 //                                                             unrotated queries with the keys' up-projection)
 //   q_plain[t, h, :] = q[t, h, 0:dn]                          (in the type that product reads)
-// turn: the pair (2i, 2i+1), i < rot/2, at position p becomes (u cos a - v sin a, v cos a + u sin a) with (cos a, sin a)
-// from the table [positions, rot/2, 2]; coordinates from `rot` on pass unchanged.  Rows without a request (slot < 0)
+// turn: the pair (2i, 2i+1) (interleaved) or (i, i + rot/2) (halves), i < rot/2, at position p becomes
+// (u cos a - v sin a, v cos a + u sin a) with (cos a, sin a) from the table [positions, rot/2, 2]; coordinates from `rot`
+// on pass unchanged.  The queries may come from a product of their own (`q_src` [T, q_ld], head by head from column 0:
+// a mixer whose queries pass a latent too) instead of from column 0 of proj.  Rows without a request (slot < 0)
 // are passed over.  float32 arithmetic throughout.
 #include "launch.cuh"
 
-__device__ __forceinline__ float latent_turn(const float* x, int e, int rot, const float* cs) {
+__device__ __forceinline__ float latent_turn(const float* x, int e, int rot, int interleaved, const float* cs) {
   if (e >= rot) return x[e];
-  const int i = e >> 1;
+  const int half = rot >> 1;
+  const bool second = interleaved ? (e & 1) : e >= half;
+  const int i = interleaved ? e >> 1 : (second ? e - half : e);
   const float c = cs[2 * i], s = cs[2 * i + 1];
-  const float u = x[2 * i], v = x[2 * i + 1];
-  return (e & 1) ? v * c + u * s : u * c - v * s;
+  const float u = interleaved ? x[2 * i] : x[i], v = interleaved ? x[2 * i + 1] : x[i + half];
+  return second ? v * c + u * s : u * c - v * s;
 }
 
 template <typename TC, typename TN>
 __global__ void __launch_bounds__(256)
-latent_encode_kernel(const float* __restrict__ proj, int ld, int kv_off, const float* __restrict__ w_latent, float eps,
-                     const float* __restrict__ cos_sin, int rot, const int* __restrict__ positions,
+latent_encode_kernel(const float* __restrict__ proj, int ld, int kv_off, const float* __restrict__ q_src, int q_ld,
+                     const float* __restrict__ w_latent, float eps,
+                     const float* __restrict__ cos_sin, int rot, int interleaved, const int* __restrict__ positions,
                      const int* __restrict__ slots, const int* __restrict__ block_table, int max_pages, int num_pages,
                      int page_size, float* __restrict__ q_wide, TN* __restrict__ q_plain, TC* __restrict__ pages, int heads,
                      int dn, int dr, int r, int store) {
@@ -37,14 +42,15 @@ latent_encode_kernel(const float* __restrict__ proj, int ld, int kv_off, const f
   if (slot < 0) return;
   const int pos = positions[t];
   const float* row = proj + (size_t)t * ld;
+  const float* qrow = q_src ? q_src + (size_t)t * q_ld : row;
   const float* cs = cos_sin + (size_t)pos * rot;  // [rot/2][2]
   const int hd = dn + dr, wide = r + dr;
   for (int c = threadIdx.x; c < heads * hd; c += blockDim.x) {
     const int h = c / hd, e = c - h * hd;
     if (e < dn)
-      q_plain[((size_t)t * heads + h) * dn + e] = ms_from_float<TN>(row[c]);
+      q_plain[((size_t)t * heads + h) * dn + e] = ms_from_float<TN>(qrow[c]);
     else
-      q_wide[((size_t)t * heads + h) * wide + r + (e - dn)] = latent_turn(row + h * hd + dn, e - dn, rot, cs);
+      q_wide[((size_t)t * heads + h) * wide + r + (e - dn)] = latent_turn(qrow + h * hd + dn, e - dn, rot, interleaved, cs);
   }
   if (!store) return;
   const float* kv = row + kv_off;
@@ -55,11 +61,11 @@ latent_encode_kernel(const float* __restrict__ proj, int ld, int kv_off, const f
   if (page < 0 || page >= num_pages) return;
   TC* dst = pages + ((size_t)page * page_size + pos % page_size) * wide;
   for (int c = threadIdx.x; c < wide; c += blockDim.x)
-    dst[c] = ms_from_float<TC>(c < r ? kv[c] * inv * w_latent[c] : latent_turn(kv + r, c - r, rot, cs));
+    dst[c] = ms_from_float<TC>(c < r ? kv[c] * inv * w_latent[c] : latent_turn(kv + r, c - r, rot, interleaved, cs));
 }
 
-MS_API int ms_latent_encode(const float* proj, int ld, int kv_off, const float* w_latent, float eps, const float* cos_sin,
-                            int rot, int table_positions, const int* positions, const int* slots, const int* block_table,
+MS_API int ms_latent_encode(const float* proj, int ld, int kv_off, const float* q_src, int q_ld, const float* w_latent, float eps,
+                            const float* cos_sin, int rot, int interleaved, int table_positions, const int* positions, const int* slots, const int* block_table,
                             int max_pages, int num_pages, int page_size, float* q_wide, void* q_plain, int plain_dtype,
                             void* pages, int cache_dtype, int tokens, int heads, int dn, int dr, int r, int store,
                             cudaStream_t stream) {
@@ -67,11 +73,12 @@ MS_API int ms_latent_encode(const float* proj, int ld, int kv_off, const float* 
   MS_REQUIRE(tokens > 0 && heads > 0 && dn > 0 && dr >= 0 && r > 0, "latent_encode: bad sizes");
   MS_REQUIRE(rot >= 0 && rot <= dr && rot % 2 == 0, "latent_encode: %d rotated coordinates of %d", rot, dr);
   MS_REQUIRE(rot == 0 || (cos_sin && table_positions > 0), "latent_encode: no table of angles");
-  MS_REQUIRE(ld >= heads * (dn + dr) && ld >= kv_off + (store ? r + dr : 0), "latent_encode: rows of %d elements are too short", ld);
+  MS_REQUIRE((q_src ? q_ld : ld) >= heads * (dn + dr) && ld >= kv_off + (store ? r + dr : 0),
+             "latent_encode: rows of %d elements are too short", ld);
   MS_REQUIRE(!store || (max_pages > 0 && num_pages > 0 && page_size > 0 && pages), "latent_encode: no cache to write");
 #define MS_LATENT(TC, TN)                                                                                                 \
   MS_LAUNCH_RESULT("latent_encode", ms_launch(latent_encode_kernel<TC, TN>, dim3(tokens), dim3(256), 0, stream, 1, true, proj, ld, \
-                                              kv_off, w_latent, eps, cos_sin, rot, positions, slots, block_table, max_pages,      \
+                                              kv_off, q_src, q_ld, w_latent, eps, cos_sin, rot, interleaved, positions, slots, block_table, max_pages,      \
                                               num_pages, page_size, q_wide, (TN*)q_plain, (TC*)pages, heads, dn, dr, r, store))
   if (cache_dtype == MS_F32 && plain_dtype == MS_F32)
     MS_LATENT(float, float);

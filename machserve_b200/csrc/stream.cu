@@ -10,6 +10,8 @@
 //   The sums and the norm are float32; the order of a row's additions depends on d alone.
 // * norm_pair_mean: out = m * (a / rms(a) * wa + b / rms(b) * wb), each rms over the row's d elements with eps inside the
 //   root: the two halves of a mixer made of two, each normed with a weight of its own, in float32.
+// * pair_weighted_sum: out = sa * (a + bias_a) + sb * (b + bias_b), the biases float32 [d] or absent: the two halves of a mixer
+//   made of two, each with a multiplier of its own (and the bias of its output projection), in float32.
 // * gated_act_mul: out[r, c] = act(gate_up[r, c]) * gate_up[r, inter + c], act = SiLU or the tanh form of GELU,
 //   computed in float32 from a float32 or bfloat16 product.
 #include "launch.cuh"
@@ -253,6 +255,51 @@ MS_API int ms_norm_pair_mean(const float* a, const float* b, const float* wa, co
   else
     MS_LAUNCH_RESULT("norm_pair_mean", ms_launch(norm_pair_mean_kernel<false>, dim3(rows), dim3(ST_THREADS), 0, stream, 1, true, a, b, wa, wb,
                                                  out, d, eps, m));
+  return 0;
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+
+template <bool VEC>
+__global__ void __launch_bounds__(256)
+pair_weighted_sum_kernel(const float* __restrict__ a, const float* __restrict__ b, const float* __restrict__ bias_a,
+                         const float* __restrict__ bias_b, float* __restrict__ out, int d, size_t total, float sa, float sb) {
+  ms_pdl_trigger();
+  ms_pdl_wait();
+  const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * (VEC ? 4 : 1);
+  if (i >= total) return;
+  if constexpr (VEC) {
+    const int c = (int)(i % d);  // (d is a multiple of 4: the four lie in one row)
+    float4 x = *reinterpret_cast<const float4*>(a + i), y = *reinterpret_cast<const float4*>(b + i);
+    if (bias_a) {
+      const float4 u = *reinterpret_cast<const float4*>(bias_a + c);
+      x.x += u.x, x.y += u.y, x.z += u.z, x.w += u.w;
+    }
+    if (bias_b) {
+      const float4 u = *reinterpret_cast<const float4*>(bias_b + c);
+      y.x += u.x, y.y += u.y, y.z += u.z, y.w += u.w;
+    }
+    *reinterpret_cast<float4*>(out + i) = make_float4(sa * x.x + sb * y.x, sa * x.y + sb * y.y, sa * x.z + sb * y.z, sa * x.w + sb * y.w);
+  } else {
+    const int c = (int)(i % d);
+    out[i] = sa * (a[i] + (bias_a ? bias_a[c] : 0.f)) + sb * (b[i] + (bias_b ? bias_b[c] : 0.f));
+  }
+}
+
+MS_API int ms_pair_weighted_sum(const float* a, const float* b, const float* bias_a, const float* bias_b, float* out, int rows, int d,
+                                float sa, float sb, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  MS_REQUIRE(rows > 0 && d > 0, "pair_weighted_sum: bad sizes rows=%d d=%d", rows, d);
+  const size_t total = (size_t)rows * d;
+  const bool vec = d % 4 == 0 && (((uintptr_t)a | (uintptr_t)b | (uintptr_t)bias_a | (uintptr_t)bias_b | (uintptr_t)out) & 15) == 0;
+  const size_t threads = vec ? total / 4 : total;
+  const unsigned blocks = (unsigned)((threads + 255) / 256);
+  if (vec)
+    MS_LAUNCH_RESULT("pair_weighted_sum", ms_launch(pair_weighted_sum_kernel<true>, dim3(blocks), dim3(256), 0, stream, 1, true, a, b, bias_a,
+                                                    bias_b, out, d, total, sa, sb));
+  else
+    MS_LAUNCH_RESULT("pair_weighted_sum", ms_launch(pair_weighted_sum_kernel<false>, dim3(blocks), dim3(256), 0, stream, 1, true, a, b, bias_a,
+                                                    bias_b, out, d, total, sa, sb));
   return 0;
 }
 

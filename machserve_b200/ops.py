@@ -125,24 +125,28 @@ class _Signatures:
     ms_glu_clamped = [P, P, I, I, I, F, F, F, P]
     ms_sigmoid_gate_mul = [P, I, P, I, P, I, I, I, P]
     ms_qk_norm_store = [P, I, P, P, F, F, I, P, P, P, I, I, I, P, P, P, P, I, I, I, I, I, I, I, P]
-    ms_latent_encode = [P, I, I, P, F, P, I, I, P, P, P, I, I, I, P, P, I, P, I, I, I, I, I, I, I, P]
+    ms_latent_encode = [P, I, I, P, I, P, F, P, I, I, I, P, P, P, I, I, I, P, P, I, P, I, I, I, I, I, I, I, P]
     ms_embed_scaled_pos = [P, I, P, P, P, P, I, I, I, I, F, P]
     ms_add_streams_rmsnorm = [P, P, I, P, I, P, P, P, P, I, P, I, I, F, F, P]
     ms_norm_pair_mean = [P, P, P, P, P, I, I, F, F, P]
+    ms_pair_weighted_sum = [P, P, P, P, P, I, I, F, F, P]
+    ms_mm_gates = [P, I, I, I, P, P, F, P, LL, LL, P, P, P, P, I, I, P]
+    ms_mm_scan = [P, I, I, I, I, P, F, P, LL, P, P, P, P, I, I, I, I, I, P]
+    ms_mm_output = [P, P, P, I, P, F, P, I, I, I, I, P]
     ms_softcap = [P, LL, F, P]
     ms_head_gate_mul = [P, P, I, P, I, I, I, I, P]
-    ms_rope_store = [P, I, P, I, I, I, P, P, P, I, I, I, P, P, P, P, I, I, I, I, I, I, I, P]
+    ms_rope_store = [P, I, P, P, I, I, I, P, P, P, I, I, I, P, P, P, P, I, I, I, I, I, I, I, P]
     ms_gdr_prepare = [P, I, I, I, I, P, I, P, P, P, LL, LL, P, P, P, P, P, I, I, I, I, I, F, P]
     ms_gdr_conv_update = [P, I, I, I, P, LL, LL, P, P, P, I, I, P]
     ms_gdr_scan = [P, P, P, LL, P, P, P, P, I, I, I, I, I, I, P]
     ms_moe_route_scored = [P, P, I, I, I, I, F, P, P, I, P]
     ms_gated_act_mul = [P, I, P, I, I, I, I, P]
-    ms_head_norm_store = [P, I, P, P, P, F, I, P, P, P, I, I, I, P, P, P, P, I, I, I, I, I, I, I, I, P]
+    ms_head_norm_store = [P, I, P, P, P, F, F, I, I, P, P, P, I, I, I, P, P, P, P, I, I, I, I, I, I, I, I, P]
     ms_attention_wide_scored = [P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, F, P, I, I, I, P]
     ms_attention_wide_mma_scored = [P, P, P, P, P, P, P, P, I, I, P, P, I, I, I, I, I, I, I, I, I, F, I, P, F, P, I, I, P]
     ms_gla_decay = [P, I, P, I, P, I, F, P, I, I, P]
     ms_gla_scan = [P, I, I, I, I, P, F, P, P, P, P, P, I, I, I, I, I, P]
-    ms_gla_output = [P, P, I, P, F, P, I, I, I, I, P]
+    ms_gla_output = [P, I, P, I, P, F, P, I, I, I, I, P]
     ms_moe_route = [P, P, I, I, P, P, I, P]
     ms_moe_gate_up_pairs = [P, P, P, P, P, P, I, I, I, I, I, I, I, P]
     ms_moe_down_pairs = [P, P, P, P, P, P, I, I, I, I, I, I, P]
@@ -1042,14 +1046,18 @@ def qk_norm_store(proj, wq, wk, eps, coef, every, positions, slot_of_token, bloc
 
 
 def latent_encode(proj, kv_off, w_latent, eps, cos_sin, rot, positions, slot_of_token, block_table, q_wide, q_plain, pages,
-                  heads: int, dn: int, dr: int, r: int, store: bool = True):
+                  heads: int, dn: int, dr: int, r: int, store: bool = True, queries=None, interleaved: bool = True):
     """Between the input product of a latent-attention mixer and its attention: the latent's unit-rms norm with weight
     and the rotated key part into the pages [pages, 1, page, r + dr]; the queries' rotated parts into q_wide[:, :, r:]
     (float32 [T, heads, r + dr]); their unrotated parts into q_plain [T, heads, dn] (the dtype their product reads).
 
     proj float32 [T, ld]: queries at column 0 head by head as [dn | dr], the down-projection [r | dr] at `kv_off`;
-    cos_sin float32 [positions, rot/2, 2]: interleaved pairs of the first `rot` of the dr coordinates are turned."""
+    cos_sin float32 [positions, rot/2, 2]: pairs of the first `rot` of the dr coordinates are turned, (2i, 2i + 1) when
+    `interleaved`, else (i, i + rot/2).  `queries` (float32 [T, >= heads*(dn + dr)], unit column stride): the queries come from
+    there instead of from column 0 of proj."""
     t = q_plain.shape[0]
+    _need(queries is None or (queries.dtype == torch.float32 and queries.stride(1) == 1 and queries.shape[0] == t
+                              and queries.shape[1] >= heads * (dn + dr)), "latent_encode: bad queries")
     _need(proj.dtype == torch.float32 and proj.stride(1) == 1 and q_wide.dtype == torch.float32 and q_wide.is_contiguous()
           and q_plain.is_contiguous() and q_wide.numel() == t * heads * (r + dr) and q_plain.numel() == t * heads * dn,
           "latent_encode: bad layout")
@@ -1061,8 +1069,8 @@ def latent_encode(proj, kv_off, w_latent, eps, cos_sin, rot, positions, slot_of_
         _need(pages.is_contiguous() and tuple(pages.shape[1:]) == (1, pages.shape[2], r + dr), "latent_encode: bad pages")
         _need(block_table.dtype == torch.int32 and block_table.is_contiguous(), "latent_encode: bad block table")
     _check(lib().ms_latent_encode(
-        _ptr(proj), proj.stride(0), int(kv_off), _ptr(w_latent), float(eps), _ptr(cos_sin), int(rot),
-        cos_sin.shape[0] if cos_sin is not None else 0, _ptr(positions), _ptr(slot_of_token), _ptr(block_table),
+        _ptr(proj), proj.stride(0), int(kv_off), _ptr(queries), queries.stride(0) if queries is not None else 0, _ptr(w_latent),
+        float(eps), _ptr(cos_sin), int(rot), int(bool(interleaved)), cos_sin.shape[0] if cos_sin is not None else 0, _ptr(positions), _ptr(slot_of_token), _ptr(block_table),
         block_table.shape[1] if store else 0, pages.shape[0] if store else 0, pages.shape[2] if store else 0, _ptr(q_wide),
         _ptr(q_plain), _code(q_plain), _ptr(pages if store else None), _code(pages) if store else _code(q_plain), t, heads, dn, dr, r,
         int(store), _stream()), "latent_encode")
@@ -1256,12 +1264,13 @@ def gated_act_mul(gate_up, out, activation: str):
 
 def head_norm_store(proj, eps: float, positions, slot_of_token, block_table, q_out, k_pages, v_pages, num_heads: int, num_kv_heads: int,
                     dk: int, dv: int, v_off: Optional[int], norm: bool = True, wq=None, wk=None, store: bool = True, q_half=None,
-                    bias=None):
+                    bias=None, temp_coef: float = 0.0, temp_every: int = 1):
     """Every query head and every key head divided by its own root mean square over dk (eps inside the root; optional
     weights wq, wk float32 [dk]; `norm` False leaves them as they are); q to q_out (float32 [T, Hq*dk]) and, optionally, to
     a bfloat16 copy; the normed keys into k_pages; into v_pages the values at column `v_off` of the product, or, `v_off`
     None, the keys as they were projected (before the norm).  proj float32 [T, >= (Hq + Hkv)*dk (+ Hkv*dv)] = [q | k | v];
-    `bias` (float32, one entry per column that is read, or None) is added to the product first."""
+    `bias` (float32, one entry per column that is read, or None) is added to the product first.  With `temp_coef` c the
+    query at position p is multiplied by 1 + c * ln(floor((p + 1) / temp_every) + 1)."""
     t = q_out.shape[0]
     _need(proj.dtype == torch.float32 and proj.stride(1) == 1 and q_out.dtype == torch.float32 and q_out.is_contiguous()
           and q_out.numel() == t * num_heads * dk, "head_norm_store: bad layout")
@@ -1277,7 +1286,8 @@ def head_norm_store(proj, eps: float, positions, slot_of_token, block_table, q_o
               and tuple(v_pages.shape[1:]) == (num_kv_heads, k_pages.shape[2], dv), "head_norm_store: bad pages")
         _need(block_table.dtype == torch.int32 and block_table.is_contiguous(), "head_norm_store: bad block table")
     _check(lib().ms_head_norm_store(
-        _ptr(proj), proj.stride(0), _ptr(bias), _ptr(wq), _ptr(wk), float(eps), int(norm), _ptr(positions), _ptr(slot_of_token),
+        _ptr(proj), proj.stride(0), _ptr(bias), _ptr(wq), _ptr(wk), float(eps), float(temp_coef), int(temp_every), int(norm),
+        _ptr(positions), _ptr(slot_of_token),
         _ptr(block_table), block_table.shape[1] if store else 0, k_pages.shape[0] if store else 0, k_pages.shape[2] if store else 0,
         _ptr(q_out), _ptr(q_half), _ptr(k_pages if store else None), _ptr(v_pages if store else None), _code(k_pages) if store else F32, t,
         num_heads, num_kv_heads, dk, dv, -1 if v_off is None else int(v_off), int(store), _stream()), "head_norm_store")
@@ -1320,14 +1330,15 @@ def gla_scan(proj, q_off: int, k_off: int, v_off: int, decay, q_scale: float, st
 
 
 def gla_output(o, gate, weight, eps: float, out, heads: int, dv: int):
-    """out = o / rms(o) * weight (per head over dv, eps inside the root) * silu(gate).  o float32 [T, heads*dv]; gate float32
-    [T, heads*dv] with unit column stride (any row stride) or None; weight float32 [dv] or None; out [T, heads*dv]."""
+    """out = o / rms(o) * weight (per head over dv, eps inside the root) * silu(gate).  o float32 [T, heads*dv] with unit
+    column stride (any row stride); gate float32 [T, heads*dv] likewise, or None; weight float32 [dv] or None; out
+    [T, heads*dv].  With one head and no gate: the RMS norm of the rows of a column range of a wider product."""
     t = o.shape[0]
-    _need(o.dtype == torch.float32 and o.is_contiguous() and out.is_contiguous() and o.shape[1] == heads * dv
+    _need(o.dtype == torch.float32 and o.stride(1) == 1 and out.is_contiguous() and o.shape[1] == heads * dv
           and tuple(out.shape) == tuple(o.shape), "gla_output: bad layout")
     _need(gate is None or (gate.dtype == torch.float32 and gate.stride(1) == 1 and gate.shape[1] == heads * dv), "gla_output: bad gate")
     _need(weight is None or (weight.dtype == torch.float32 and weight.numel() == dv), "gla_output: bad weight")
-    _check(lib().ms_gla_output(_ptr(o), _ptr(gate), gate.stride(0) if gate is not None else 0, _ptr(weight), float(eps), _ptr(out),
+    _check(lib().ms_gla_output(_ptr(o), o.stride(0), _ptr(gate), gate.stride(0) if gate is not None else 0, _ptr(weight), float(eps), _ptr(out),
                                _code(out), t, heads, dv, _stream()), "gla_output")
     return out
 
@@ -1342,6 +1353,75 @@ def norm_pair_mean(a, b, wa, wb, out, eps: float, scale: float = 0.5):
     _need(all(x.dtype == torch.float32 and x.is_contiguous() and tuple(x.shape) == (t, d) for x in (a, b, out)), "norm_pair_mean: bad rows")
     _need(all(w.dtype == torch.float32 and w.is_contiguous() and w.numel() == d for w in (wa, wb)), "norm_pair_mean: bad weights")
     _check(lib().ms_norm_pair_mean(_ptr(a), _ptr(b), _ptr(wa), _ptr(wb), _ptr(out), t, d, float(eps), float(scale), _stream()), "norm_pair_mean")
+    return out
+
+
+def pair_weighted_sum(a, b, out, scale_a: float, scale_b: float, bias_a=None, bias_b=None):
+    """out = scale_a * (a + bias_a) + scale_b * (b + bias_b) in float32.  a, b, out float32 [T, d]; the biases float32 [d] or None."""
+    t, d = out.shape
+    _need(all(x.dtype == torch.float32 and x.is_contiguous() and tuple(x.shape) == (t, d) for x in (a, b, out)), "pair_weighted_sum: bad rows")
+    _need(all(v is None or (v.dtype == torch.float32 and v.is_contiguous() and v.numel() == d) for v in (bias_a, bias_b)),
+          "pair_weighted_sum: bad biases")
+    _check(lib().ms_pair_weighted_sum(_ptr(a), _ptr(b), _ptr(bias_a), _ptr(bias_b), _ptr(out), t, d, float(scale_a), float(scale_b), _stream()),
+           "pair_weighted_sum")
+    return out
+
+
+# ------------------------------------------------------------------------------------------- the matrix memory (mLSTM cell)
+
+
+def mm_state_floats(heads: int, dk: int, dv: int) -> int:
+    """Floats of one request's state: per head the matrix with the normalizer as one more column, then the heads' stabilizers."""
+    return heads * dk * (dv + 1) + heads
+
+
+def mm_gates(proj, i_off: int, f_off: int, bias_i, bias_f, cap: float, state, cu_tokens, state_slots, slot_of_token, gates, seqs: int,
+             heads: int, dk: int, dv: int):
+    """The gates of a matrix memory over the rows of the step, sequence by sequence, in order: i = cap tanh(x_i / cap),
+    f = logsigmoid(cap tanh(x_f / cap)), m_t = max(f_t + m_(t-1), i_t) from the m the slot holds (which is advanced),
+    gates[t, h] = (exp(f_t + m_(t-1) - m_t), exp(i_t - m_t), m_t, 0).  proj float32 [T, ld] holds x_i at columns i_off + h and
+    x_f at f_off + h; the biases float32 [heads] or None; state float32 [slots, mm_state_floats]; gates float32 [T, heads, 4]."""
+    _need(proj.dtype == torch.float32 and proj.stride(1) == 1 and gates.dtype == torch.float32 and gates.is_contiguous()
+          and gates.numel() == proj.shape[0] * heads * 4, "mm_gates: bad layout")
+    _need(state.dtype == torch.float32 and state.is_contiguous() and state.dim() == 2 and state.shape[1] == mm_state_floats(heads, dk, dv),
+          "mm_gates: bad state")
+    _need(all(b is None or (b.dtype == torch.float32 and b.numel() == heads) for b in (bias_i, bias_f)), "mm_gates: bad biases")
+    _need(cu_tokens.numel() >= seqs + 1 and state_slots.numel() >= seqs, "mm_gates: bad sequence lists")
+    _check(lib().ms_mm_gates(_ptr(proj), proj.stride(0), int(i_off), int(f_off), _ptr(bias_i), _ptr(bias_f), float(cap), _ptr(state),
+                             state.stride(0), heads * dk * (dv + 1), _ptr(cu_tokens), _ptr(state_slots), _ptr(slot_of_token), _ptr(gates),
+                             int(seqs), heads, _stream()), "mm_gates")
+    return gates
+
+
+def mm_scan(proj, q_off: int, k_off: int, v_off: int, gates, q_scale: float, state, cu_tokens, state_slots, slot_of_token, out, seqs: int,
+            heads: int, dk: int, dv: int, narrow: bool = False):
+    """The recurrence S <- a_t S + b_t k_t v_t^T, n <- a_t n + b_t k_t per sequence and head over the rows of the step in
+    order, from and to `state`; out[t, h, :dv] = S^T (q_t * q_scale), out[t, h, dv] = n . (q_t * q_scale).  proj float32 [T, ld]
+    holds q, k (heads*dk each) and v (heads*dv) at the column offsets; gates float32 [T, heads, 4] as `mm_gates` leaves them;
+    out float32 [T, heads, dv + 1].  `narrow`: blocks of 8 columns instead of 32 (for steps with long portions); same bits."""
+    _need(proj.dtype == torch.float32 and proj.stride(1) == 1 and gates.dtype == torch.float32 and gates.is_contiguous()
+          and out.dtype == torch.float32 and out.is_contiguous() and out.numel() == proj.shape[0] * heads * (dv + 1), "mm_scan: bad layout")
+    _need(state.dtype == torch.float32 and state.is_contiguous() and state.dim() == 2 and state.shape[1] == mm_state_floats(heads, dk, dv),
+          "mm_scan: bad state")
+    _need(cu_tokens.numel() >= seqs + 1 and state_slots.numel() >= seqs, "mm_scan: bad sequence lists")
+    _check(lib().ms_mm_scan(_ptr(proj), proj.stride(0), int(q_off), int(k_off), int(v_off), _ptr(gates), float(q_scale), _ptr(state),
+                            state.stride(0), _ptr(cu_tokens), _ptr(state_slots), _ptr(slot_of_token), _ptr(out), int(seqs), heads, dk, dv,
+                            int(narrow), _stream()), "mm_scan")
+    return out
+
+
+def mm_output(o, gates, gate, weight, eps: float, out, heads: int, dv: int):
+    """y = o[..., :dv] / (max(|o[..., dv]|, exp(-m)) + 1e-6), then out = y / rms(y) (per head over dv, eps inside the root)
+    * weight * sigmoid(gate).  o float32 [T, heads, dv + 1] and gates float32 [T, heads, 4] as `mm_scan` and `mm_gates` leave
+    them; gate float32 [T, heads*dv] with unit column stride (any row stride) or None; weight float32 [heads*dv] or None."""
+    t = out.shape[0]
+    _need(o.dtype == torch.float32 and o.is_contiguous() and o.numel() == t * heads * (dv + 1) and out.is_contiguous()
+          and tuple(out.shape) == (t, heads * dv) and gates.dtype == torch.float32 and gates.is_contiguous()
+          and gates.numel() == t * heads * 4, "mm_output: bad layout")
+    _need(gate is None or (gate.dtype == torch.float32 and gate.stride(1) == 1 and gate.shape[1] == heads * dv), "mm_output: bad gate")
+    _need(weight is None or (weight.dtype == torch.float32 and weight.numel() == heads * dv), "mm_output: bad weight")
+    _check(lib().ms_mm_output(_ptr(o), _ptr(gates), _ptr(gate), gate.stride(0) if gate is not None else 0, _ptr(weight), float(eps),
+                              _ptr(out), _code(out), t, heads, dv, _stream()), "mm_output")
     return out
 
 
@@ -1364,12 +1444,15 @@ def head_gate_mul(x, gate, out, heads: int, dv: int):
 
 
 def rope_store(proj, cos_sin, rot: int, interleaved: bool, positions, slot_of_token, block_table, q_out, k_pages, v_pages, num_heads: int,
-               num_kv_heads: int, dk: int, dv: int, store: bool = True, q_half=None):
+               num_kv_heads: int, dk: int, dv: int, store: bool = True, q_half=None, bias=None):
     """The first `rot` coordinates of every query and key head turned by the table's angles at the row's position (pairs
     (i, i + rot/2), or (2i, 2i + 1) when `interleaved`); q to q_out (float32 [T, Hq*dk]) and, optionally, to a bfloat16 copy;
     the turned keys into k_pages [pages, Hkv, page, dk] and the values into v_pages [pages, Hkv, page, dv].  proj float32
-    [T, >= Hq*dk + Hkv*(dk + dv)] = [q | k | v]; cos_sin float32 [positions, rot/2, 2] (None when rot is 0)."""
+    [T, >= Hq*dk + Hkv*(dk + dv)] = [q | k | v]; cos_sin float32 [positions, rot/2, 2] (None when rot is 0); `bias` (float32,
+    one entry per column of q | k | v, or None) is added to the product as it is read."""
     t = q_out.shape[0]
+    _need(bias is None or (bias.dtype == torch.float32 and bias.is_contiguous()
+                           and bias.numel() == num_heads * dk + num_kv_heads * (dk + dv)), "rope_store: bad bias")
     _need(proj.dtype == torch.float32 and proj.stride(1) == 1 and q_out.dtype == torch.float32 and q_out.is_contiguous()
           and q_out.numel() == t * num_heads * dk, "rope_store: bad layout")
     _need(q_half is None or (q_half.dtype == torch.bfloat16 and q_half.is_contiguous() and q_half.numel() == q_out.numel()),
@@ -1382,7 +1465,7 @@ def rope_store(proj, cos_sin, rot: int, interleaved: bool, positions, slot_of_to
               and tuple(v_pages.shape[1:]) == (num_kv_heads, k_pages.shape[2], dv), "rope_store: bad pages")
         _need(block_table.dtype == torch.int32 and block_table.is_contiguous(), "rope_store: bad block table")
     _check(lib().ms_rope_store(
-        _ptr(proj), proj.stride(0), _ptr(cos_sin if rot else None), int(rot), int(bool(interleaved)), cos_sin.shape[0] if rot else 0,
+        _ptr(proj), proj.stride(0), _ptr(bias), _ptr(cos_sin if rot else None), int(rot), int(bool(interleaved)), cos_sin.shape[0] if rot else 0,
         _ptr(positions), _ptr(slot_of_token), _ptr(block_table), block_table.shape[1] if store else 0, k_pages.shape[0] if store else 0,
         k_pages.shape[2] if store else 0, _ptr(q_out), _ptr(q_half), _ptr(k_pages if store else None), _ptr(v_pages if store else None),
         _code(k_pages) if store else F32, t, num_heads, num_kv_heads, dk, dv, int(store), _stream()), "rope_store")

@@ -38,8 +38,11 @@ class PreNormBlock(Block):
         self.scale = float(spec.block_params.get("residual_scale", 1.0))
         if (feed_forward is None) != (ff_norm is None):
             raise ValueError("a pre-norm layer has a feed-forward and its norm, or neither")
-        if self.scale != 1.0 or feed_forward is None:
-            # the few-row path is the only thing the block launches beyond its parts' kernels
+        from .base import Part
+
+        joins = [type(p).fuse_norm is not Part.fuse_norm for p in (mixer, feed_forward) if p is not None]
+        if self.scale != 1.0 or feed_forward is None or not any(joins):
+            # the few-row path is the only thing the block launches beyond its parts' kernels, and no part here joins it
             self.kernel_files = ()
 
     def bind(self, tensors, rt):

@@ -7,12 +7,13 @@ import torch
 from .. import ops
 from . import wide_attend
 from ..weights.loader import TensorDecl
-from .base import POSITION_ENCODINGS, CachePlane, Mixer, PagedCache, matrix, register_mixer
+from .base import POSITION_ENCODINGS, CachePlane, Mixer, PagedCache, matrix, register_mixer, vector_f32
 
 
 @register_mixer("rotary_gated_attention")
 class RotaryGatedAttention(wide_attend.WideAttendPlan, Mixer):
-    """q = Wq x (heads x key_dim), k = Wk x (kv_heads x key_dim), v = Wv x (kv_heads x value_dim), no biases; the position
+    """q = Wq x (heads x key_dim), k = Wk x (kv_heads x key_dim), v = Wv x (kv_heads x value_dim), with `bias` each plus a
+    bias of its own (added in float32 where the product is read); the position
     encoding (a rotary one over the first rotary_dim coordinates of every query and key head, or none) turns q and k; query
     head h reads key/value head h // (heads / kv_heads); score = scale * q . k over the keys 0..p (or the last `window`,
     the query's own among them).  With `sink` the softmax's denominator has one more term of score zero that has no value:
@@ -24,7 +25,8 @@ class RotaryGatedAttention(wide_attend.WideAttendPlan, Mixer):
     the tensor core (bfloat16 runtime, widths the tensor-core kernels cover); the delta is float32.
 
     params: prefix, hidden_size, num_heads, num_kv_heads, key_dim, value_dim, scale, window (or None), sink (bool),
-    head_gate (bool), position (a PartSpec of a rotary encoding, or None).  Tensors under the prefix: q, k, v, o, g [heads, hidden].
+    head_gate (bool), bias (bool: q.b, k.b, v.b), position (a PartSpec of a rotary encoding, or None).  Tensors under the
+    prefix: q, k, v, o, g [heads, hidden], (q.b, k.b, v.b).
     """
 
     graph_safe = True
@@ -42,6 +44,7 @@ class RotaryGatedAttention(wide_attend.WideAttendPlan, Mixer):
         self.scale = float(spec["scale"])
         self.window = spec.get("window")
         self.has_sink, self.has_gate = bool(spec.get("sink", True)), bool(spec.get("head_gate", True))
+        self.has_bias = bool(spec.get("bias", False))
         self.position = POSITION_ENCODINGS.build(spec["position"]) if spec.get("position") is not None else None
         self.qw, self.kw, self.vw = self.hq * self.dk, self.hkv * self.dk, self.hkv * self.dv
         files = ["rope_store", "gated", "attention_wide", "attention_wide_mma"]
@@ -60,6 +63,9 @@ class RotaryGatedAttention(wide_attend.WideAttendPlan, Mixer):
         ]
         if self.has_gate:
             out.append(TensorDecl(p + "g", (self.hq, self.hidden)))
+        if self.has_bias:
+            out += [TensorDecl(p + "q.b", (self.qw,), init="bias"), TensorDecl(p + "k.b", (self.kw,), init="bias"),
+                    TensorDecl(p + "v.b", (self.vw,), init="bias")]
         if self.position is not None:
             out += self.position.tensors()
         return out
@@ -70,6 +76,7 @@ class RotaryGatedAttention(wide_attend.WideAttendPlan, Mixer):
         inputs = [tensors[p + "q"], tensors[p + "k"], tensors[p + "v"]] + ([tensors[p + "g"]] if self.has_gate else [])
         self.w_in = matrix(torch.cat(inputs, dim=0), rt)
         self.w_o = matrix(tensors[p + "o"], rt)
+        self.b_in = vector_f32(torch.cat([tensors[p + n].float() for n in ("q.b", "k.b", "v.b")])) if self.has_bias else None
         self.sinks = torch.zeros(self.hq, dtype=torch.float32, device=rt.device) if self.has_sink else None
         self.table, self.rot, self.interleaved = None, 0, False
         if self.position is not None:
@@ -97,7 +104,7 @@ class RotaryGatedAttention(wide_attend.WideAttendPlan, Mixer):
         tcgen05 = self.fast and ctx.max_query_len > 1 and wide_attend.tcgen05_covers(rt, self.dk, self.dv, k_pages.shape[2])
         q_half = ws.get("rg_attn.q_half", (t, self.qw), rt.dtype) if tcgen05 or self.cluster is not None else None
         ops.rope_store(proj, self.table, self.rot, self.interleaved, ctx.positions, ctx.slot_of_token, table, q, k_pages, v_pages,
-                       self.hq, self.hkv, self.dk, self.dv, store=owns_cache, q_half=q_half)
+                       self.hq, self.hkv, self.dk, self.dv, store=owns_cache, q_half=q_half, bias=self.b_in)
         out = ws.get("rg_attn.out", (t, self.hq * self.dv), rt.dtype)
         wide_attend.attend(ctx, rt, self.fast, table, q, k_pages, v_pages, out, self.sinks, self.hq, self.hkv, self.dk, self.dv,
                            self.window, self.scale, q_half=q_half, tcgen05=tcgen05, cluster=self.cluster)

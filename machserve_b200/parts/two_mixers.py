@@ -1,5 +1,5 @@
 """A mixer made of two mixers that read the same rows: each output normed over the width with a weight of its own, then
-their mean."""
+their mean; or the two outputs as they are, each times a number of its own, then their sum."""
 from __future__ import annotations
 
 import torch
@@ -15,16 +15,25 @@ class TwoMixers(Mixer):
     mixers of any registered kind, built from their own specs; each root mean square runs over the model width (eps inside
     the root); `scale` is 1/2 unless said.  Each member keeps what it keeps (`CacheSet`: pages for one, a state for the
     other, or anything else); the members' work lists are the members' own.  In a captured step the two members run as two
-    branches of the graph.
+    branches of the graph.  With `combine` "weighted_sum" there are no norms: delta = left_scale * left(x) + right_scale *
+    right(x), in float32 (a member that offers `defer_output_bias` has its output projection's bias added here).
 
-    params: left, right (PartSpecs of mixers), left_norm, right_norm (tensor names of the weights), hidden_size, eps, scale.
+    params: left, right (PartSpecs of mixers), hidden_size, combine ("normed_mean" if absent, or "weighted_sum"); for the
+    mean: left_norm, right_norm (tensor names of the weights), eps, scale; for the sum: left_scale, right_scale.
     """
 
     def __init__(self, spec):
         super().__init__(spec)
         self.left, self.right = MIXERS.build(spec["left"]), MIXERS.build(spec["right"])
-        self.left_name, self.right_name = spec["left_norm"], spec["right_norm"]
-        self.hidden, self.eps, self.scale = int(spec["hidden_size"]), float(spec["eps"]), float(spec.get("scale", 0.5))
+        self.combine = spec.get("combine", "normed_mean")
+        if self.combine not in ("normed_mean", "weighted_sum"):
+            raise ValueError(f"two_mixers: combine '{self.combine}' is neither 'normed_mean' nor 'weighted_sum'")
+        self.hidden = int(spec["hidden_size"])
+        if self.combine == "normed_mean":
+            self.left_name, self.right_name = spec["left_norm"], spec["right_norm"]
+            self.eps, self.scale = float(spec["eps"]), float(spec.get("scale", 0.5))
+        else:
+            self.left_scale, self.right_scale = float(spec["left_scale"]), float(spec["right_scale"])
         self.graph_safe = bool(self.left.graph_safe and self.right.graph_safe)
         files = [m.kernel_files for m in (self.left, self.right)]
         self.kernel_files = None if any(f is None for f in files) else tuple(sorted({"stream", *files[0], *files[1]}))
@@ -36,6 +45,8 @@ class TwoMixers(Mixer):
         return CacheSet((self.left.cache_need(), self.right.cache_need()))
 
     def tensors(self):
+        if self.combine == "weighted_sum":
+            return [*self.left.tensors(), *self.right.tensors()]
         return [*self.left.tensors(), *self.right.tensors(), TensorDecl(self.left_name, (self.hidden,), init="scale"),
                 TensorDecl(self.right_name, (self.hidden,), init="scale")]
 
@@ -44,7 +55,10 @@ class TwoMixers(Mixer):
         self.left.bind(tensors, rt)
         self.right.bind(tensors, rt)
         self.graph_safe = bool(self.left.graph_safe and self.right.graph_safe)
-        self.w_left, self.w_right = vector_f32(tensors[self.left_name]), vector_f32(tensors[self.right_name])
+        if self.combine == "normed_mean":
+            self.w_left, self.w_right = vector_f32(tensors[self.left_name]), vector_f32(tensors[self.right_name])
+        else:  # a member's output bias rides in the sum's kernel
+            self.bias_left, self.bias_right = (getattr(m, "defer_output_bias", lambda: None)() for m in (self.left, self.right))
 
     # the members' work lists (at most one key between them)
     def plan_key(self):
@@ -70,4 +84,6 @@ class TwoMixers(Mixer):
             a = self.left.forward(ctx, x, left_cache, owns_cache)
             b = self.right.forward(ctx, x, right_cache, owns_cache)
         delta = rt.workspace.get("two_mixers.delta", (t, self.hidden), torch.float32)
+        if self.combine == "weighted_sum":
+            return ops.pair_weighted_sum(a, b, delta, self.left_scale, self.right_scale, self.bias_left, self.bias_right)
         return ops.norm_pair_mean(a, b, self.w_left, self.w_right, delta, self.eps, self.scale)
