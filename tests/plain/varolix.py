@@ -5,7 +5,8 @@ in float64, and imports nothing from the engine package: it is what the engine i
 
 Notation: d the model width, T the tokens of the sequence, p the position of a token (from 0), W [out, in] a matrix
 applied as x . W^T.  `rnd`, where a function takes it, rounds what an engine hands on in fewer bits (keys and values that
-are kept for later tokens, rows that output projections read); None rounds nothing.
+are kept for later tokens, rows that output projections read); None rounds nothing.  `rec` likewise disturbs what enters and
+leaves a recurrence, which an engine computes in 32 bits: a test finds with it the rows whose result hangs on the last bits.
 """
 from __future__ import annotations
 
@@ -96,14 +97,17 @@ def causal_softmax(s, sink=None):
     return e / den
 
 
-def grouped_attend(q, k, v, scale):
-    """q [T, H, dk], k [T, G, dk], v [T, G, dv] -> [T, H*dv]; query head h reads key/value head h // (H/G)."""
+def grouped_attend(q, k, v, scale, rnd=None):
+    """q [T, H, dk], k [T, G, dk], v [T, G, dv] -> [T, H*dv]; query head h reads key/value head h // (H/G).  `rnd` rounds the
+    queries and the softmax's weights (a tensor core's operands)."""
+    rnd = rnd or _same
     t, H, _ = q.shape
     G = k.shape[1]
     out = np.zeros((t, H, v.shape[2]))
+    q = rnd(q)
     for h in range(H):
         g = h // (H // G)
-        out[:, h] = causal_softmax(q[:, h] @ k[:, g].T * scale) @ v[:, g]
+        out[:, h] = rnd(causal_softmax(q[:, h] @ k[:, g].T * scale)) @ v[:, g]
     return out.reshape(t, -1)
 
 
@@ -116,7 +120,7 @@ def rotary_attention(h, w, p, cfg, rnd=None):
     q = rotate_half((h @ w[p + "q"].T + w[p + "q.b"]).reshape(t, H, dk), pos, cfg.get("rot"))
     k = rotate_half((h @ w[p + "k"].T + w[p + "k.b"]).reshape(t, G, dk), pos, cfg.get("rot"))
     v = (h @ w[p + "v"].T + w[p + "v.b"]).reshape(t, G, dv)
-    return rnd(grouped_attend(q, rnd(k), rnd(v), cfg["scale"])) @ w[p + "o"].T
+    return rnd(grouped_attend(q, rnd(k), rnd(v), cfg["scale"], rnd)) @ w[p + "o"].T
 
 
 def query_temperature(positions, temp):
@@ -136,7 +140,7 @@ def normed_attention(h, w, p, cfg, eps, rnd=None):
     v = (h @ w[p + "v"].T + w[p + "v.b"]).reshape(t, G, dv)
     if cfg.get("q_temp"):
         q = q * query_temperature(np.arange(t), cfg["q_temp"])[:, None, None]
-    return rnd(grouped_attend(q, rnd(k), rnd(v), cfg["scale"])) @ w[p + "o"].T + w[p + "o.b"]
+    return rnd(grouped_attend(q, rnd(k), rnd(v), cfg["scale"], rnd)) @ w[p + "o"].T + w[p + "o.b"]
 
 
 # ------------------------------------------------------------------------------------------ matrix memory
@@ -169,26 +173,27 @@ def memory_gates(h, w, p, cap):
     return soft_cap(h @ w[p + "i"].T + w[p + "i.b"], cap), log_sigmoid(soft_cap(h @ w[p + "f"].T + w[p + "f.b"], cap))
 
 
-def matrix_memory_mixer(h, w, p, cfg, eps, rnd=None):
+def matrix_memory_mixer(h, w, p, cfg, eps, rnd=None, rec=None):
     """The right half of mixer `parallel`."""
-    rnd = rnd or _same
+    rnd, rec = rnd or _same, rec or _same
     t = h.shape[0]
     H, dk, dv = cfg["heads"], cfg["dim"], cfg["vdim"]
-    q = (h @ w[p + "q"].T).reshape(t, H, dk) * dk ** -0.5
-    k = (h @ w[p + "k"].T).reshape(t, H, dk)
-    v = (h @ w[p + "v"].T).reshape(t, H, dv)
+    q = rec((h @ w[p + "q"].T).reshape(t, H, dk) * dk ** -0.5)
+    k = rec((h @ w[p + "k"].T).reshape(t, H, dk))
+    v = rec((h @ w[p + "v"].T).reshape(t, H, dv))
     i_log, f_log = memory_gates(h, w, p, cfg["gate_cap"])
+    i_log, f_log = rec(i_log), rec(f_log)
     o = np.zeros((t, H, dv))
     for head in range(H):
         o[:, head], _ = matrix_memory(q[:, head], k[:, head], v[:, head], i_log[:, head], f_log[:, head])
-    y = unit_rms(o, eps).reshape(t, H * dv) * w[p + "norm"] * sigmoid(h @ w[p + "g"].T)
+    y = unit_rms(rec(o), eps).reshape(t, H * dv) * w[p + "norm"] * sigmoid(h @ w[p + "g"].T)
     return rnd(y) @ w[p + "o"].T
 
 
-def two_mixers_sum(h, w, p, cfg, eps, rnd=None):
+def two_mixers_sum(h, w, p, cfg, eps, rnd=None, rec=None):
     """Mixer `parallel`: both halves read h; left_scale * left + right_scale * right."""
     left = normed_attention(h, w, p + "left.", cfg["left"], eps, rnd)
-    right = matrix_memory_mixer(h, w, p + "right.", cfg["right"], eps, rnd)
+    right = matrix_memory_mixer(h, w, p + "right.", cfg["right"], eps, rnd, rec)
     return cfg["left_scale"] * left + cfg["right_scale"] * right
 
 
@@ -205,7 +210,7 @@ def latent_attention(h, w, p, cfg, eps, rnd=None):
     rot = dict(cfg["rot"])
     cq = rms_norm(h @ w[p + "dq"].T, w[p + "dq.norm"], eps)
     q = (rnd(cq) @ w[p + "uq"].T).reshape(t, H, dn + dr)
-    q_plain, q_rot = q[..., :dn], rotate_half(q[..., dn:], pos, rot)
+    q_plain, q_rot = rnd(q[..., :dn]), rnd(rotate_half(q[..., dn:], pos, rot))
     down = h @ w[p + "dkv"].T
     c = rnd(rms_norm(down[:, :r], w[p + "dkv.norm"], eps))
     k_rot = rnd(rotate_half(down[:, None, r:], pos, rot)[:, 0])  # [T, dr], shared by the heads
@@ -215,7 +220,7 @@ def latent_attention(h, w, p, cfg, eps, rnd=None):
     out = np.zeros((t, H, dv))
     for head in range(H):
         s = (q_plain[:, head] @ k_plain[:, head].T + q_rot[:, head] @ k_rot.T) * cfg["scale"]
-        out[:, head] = causal_softmax(s, float(w[p + "sink"][head])) @ v[:, head] * gate[:, head:head + 1]
+        out[:, head] = rnd(causal_softmax(s, float(w[p + "sink"][head]))) @ v[:, head] * gate[:, head:head + 1]
     return rnd(out.reshape(t, H * dv)) @ w[p + "o"].T
 
 
@@ -227,21 +232,21 @@ def dense_mlp(h, w, p, rnd=None):
     return rnd(gelu_tanh(h @ w[p + "gate"].T) * (h @ w[p + "up"].T)) @ w[p + "down"].T
 
 
-def mixer(h, w, p, spec, eps, rnd=None):
+def mixer(h, w, p, spec, eps, rnd=None, rec=None):
     if spec["type"] == "attention":
         return rotary_attention(h, w, p, spec["mixer"], rnd)
     if spec["type"] == "parallel":
-        return two_mixers_sum(h, w, p, spec["mixer"], eps, rnd)
+        return two_mixers_sum(h, w, p, spec["mixer"], eps, rnd, rec)
     if spec["type"] == "latent_attention":
         return latent_attention(h, w, p, spec["mixer"], eps, rnd)
     raise ValueError(spec["type"])
 
 
-def layer(x, w, i, spec, eps, round_h=None, rnd=None):
+def layer(x, w, i, spec, eps, round_h=None, rnd=None, rec=None):
     """x <- x + mixer(norm1(x)); then, if the layer has a feed-forward, x <- x + ff(norm2(x))."""
     p = f"l{i}."
     rh = round_h or _same
-    x = x + mixer(rh(rms_norm(x, w[p + "norm1"], eps)), w, p + "mix.", spec, eps, rnd)
+    x = x + mixer(rh(rms_norm(x, w[p + "norm1"], eps)), w, p + "mix.", spec, eps, rnd, rec)
     if spec.get("mlp") is not None:
         x = x + dense_mlp(rh(rms_norm(x, w[p + "norm2"], eps)), w, p + "mlp.", rnd)
     return x
@@ -256,13 +261,13 @@ def run_order(config):
     return list(range(loop["start"])) + list(range(loop["start"], loop["stop"])) * loop["times"] + list(range(loop["stop"], n))
 
 
-def forward(config, w, tokens, taps=None, round_h=None, round_inner=None):
+def forward(config, w, tokens, taps=None, round_h=None, round_inner=None, round_rec=None):
     """Logits [T, vocab] of a whole sequence; `taps`, a list, receives the stream after every run of a layer."""
     w = {k: np.asarray(v, dtype=np.float64) if np.asarray(v).dtype.kind == "f" else np.asarray(v) for k, v in w.items()}
     eps = config["norm"]["eps"]
     x = w["embed"][np.asarray(tokens, dtype=np.int64)]
     for i in run_order(config):
-        x = layer(x, w, i, config["layers"][i], eps, round_h, round_inner)
+        x = layer(x, w, i, config["layers"][i], eps, round_h, round_inner, round_rec)
         if taps is not None:
             taps.append(x.copy())
     return rms_norm(x, w["final.norm"], eps) @ w["head"].T
