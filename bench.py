@@ -39,6 +39,12 @@ one more in the softmax's denominator and head gates beside a gated delta rule, 
 without a gate behind a router of sigmoid scores with groups) beside the Fozutar design and the dense decoder at the same
 sizes, and its kernels alone beside the like kernels of those.
 
+`--only varolix` (not part of the default run either) times the Varolix design (rotary attention with biases and stretched
+waves; normed attention with a query temperature beside a matrix memory with exponential gates, summed with weights; latent
+attention with a query latent, a sink and head gates; dense gated feed-forwards) beside the Fozutar design (the closest one:
+attention layers and layers with a matrix state, dense feed-forwards among its layers) and the dense decoder at the same
+sizes, and its kernels alone beside the like kernels of those.
+
 This engine runs on one GPU: for --gpus > 1 it says so and exits with 2.
 
     python bench.py --kernel attention_prefill
@@ -1149,6 +1155,221 @@ def workload_modadra(a, pk):
             "data": "random-init weights drawn on the device, seeded uniform random token ids", "peaks": pk["source"], "sizes": out}
 
 
+def varolix_config(raw, layers):
+    """A Varolix configuration with the layer sizes of the Qwen2 shape `raw`: the same width, vocabulary, feed-forward, heads,
+    key heads and head size.  Layers in turns of three: rotary attention (half of every head rotated, waves stretched four
+    times past 2,048 positions); normed attention beside a matrix memory of half as many heads of twice the head size in
+    their values; latent attention (a latent of four head sizes, a rotated part of half a head size, a query latent of six
+    head sizes).  No loop."""
+    d, i, v, hq, hkv, hd = sizes(raw)
+    att = {"heads": hq, "kv_heads": hkv, "dim": hd, "vdim": hd, "scale": hd ** -0.5,
+           "rot": {"dims": hd // 2, "base": 10000.0, "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}
+    pair = {"left": {"heads": hq, "kv_heads": hkv, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "q_temp": {"coef": 0.1, "every": 1024}},
+            "right": {"heads": max(1, hq // 2), "dim": hd, "vdim": 2 * hd, "gate_cap": 15.0}, "left_scale": 1.0, "right_scale": 0.5}
+    lat = {"heads": hq, "dim": hd, "rot_dim": hd // 2, "vdim": hd, "kv_rank": 4 * hd, "q_rank": 6 * hd, "scale": (1.5 * hd) ** -0.5,
+           "rot": {"dims": hd // 2, "base": 10000.0}}
+    kinds = [("attention", att), ("parallel", pair), ("latent_attention", lat)]
+    return {"architecture": "Varolix", "vocab": v, "width": d, "norm": {"eps": 1e-6},
+            "layers": [{"type": kinds[n % 3][0], "mixer": kinds[n % 3][1], "mlp": {"kind": "dense", "ff": i}} for n in range(layers)]}
+
+
+def time_varolix_kernels(torch, ops, raw, pk):
+    """The Varolix design's kernels alone, each beside the like kernel of the closest designs at equal sizes where there is
+    one (inputs larger than the L2; a CUDA graph of a few launches between events)."""
+    d, inter, _, hq, hkv, hd = sizes(raw)
+    dev, bf = "cuda:0", torch.bfloat16
+    g = torch.Generator(device=dev).manual_seed(0)
+    rnd = lambda *shape, dt=torch.float32, scale=1.0: (torch.randn(*shape, device=dev, generator=g) * scale).to(dt)
+
+    def us(fn, reps=5):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(reps):
+                fn()
+        graph.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps * 1000
+
+    out = {}
+
+    def entry(name, t_new, t_like=None, nbytes=None, flops=None, like_bytes=None, like_flops=None, like="(no like kernel)"):
+        e = {"us": round(t_new, 1), "like": like}
+        if t_like is not None:
+            e["like_us"] = round(t_like, 1)
+        if nbytes:
+            e["hbm_frac"] = round(nbytes / t_new / 1e3 / pk["hbm_gbs"], 3)
+            if t_like is not None:
+                e["like_hbm_frac"] = round((like_bytes or nbytes) / t_like / 1e3 / pk["hbm_gbs"], 3)
+        if flops:
+            e["tensor_frac"] = round(flops / t_new / 1e6 / pk["bf16_tflops"], 4)
+            if t_like is not None:
+                e["like_tensor_frac"] = round((like_flops or flops) / t_like / 1e6 / pk["bf16_tflops"], 4)
+        out[name] = e
+
+    # the weighted sum of the two mixers' outputs (with the left one's output bias): 32,768 rows
+    rows = 32768
+    da, db, res = rnd(rows, d), rnd(rows, d), rnd(rows, d)
+    w = rnd(d)
+    o32, o16 = torch.empty(rows, d, device=dev), torch.empty(rows, d, dtype=bf, device=dev)
+    t_new = us(lambda: ops.pair_weighted_sum(da, db, o32, 1.2, 0.9, bias_a=w))
+    t_like = us(lambda: ops.norm_pair_mean(da, db, w, w, o32, 1e-6, 0.5))
+    entry("pair_weighted_sum", t_new, t_like, rows * d * 12, like="norm_pair_mean (the mean of two normed rows)")
+    del da, db, res, o32, o16
+    # between the input product and the attention: 16,384 rows
+    rows, page = 16384, PAGE
+    pos = (torch.arange(rows, dtype=torch.int32, device=dev) % 4096).contiguous()
+    slot = (torch.arange(rows, dtype=torch.int32, device=dev) // 4096).contiguous()
+    pages = rows // page
+    table = torch.arange(pages, dtype=torch.int32, device=dev).view(4, -1).contiguous()
+    qkvw = (hq + 2 * hkv) * hd
+    proj, bias = rnd(rows, qkvw), rnd(qkvw)
+    kp, vp = torch.zeros(pages, hkv, page, hd, dtype=bf, device=dev), torch.zeros(pages, hkv, page, hd, dtype=bf, device=dev)
+    qo, qh = torch.empty(rows, hq * hd, device=dev), torch.empty(rows, hq * hd, dtype=bf, device=dev)
+    half = torch.zeros(4096, hd // 4, 2, device=dev)
+    proj16, qo16 = rnd(rows, qkvw, dt=bf), torch.empty(rows, hq * hd, dtype=bf, device=dev)
+    ang = torch.zeros(4096, hd // 2, 2, device=dev)
+    t_like = us(lambda: ops.rope_kv_store(proj16, None, pos, slot, table, ang, hd, False, qo16, kp, vp, hq, hkv, hd))
+    store_bytes = rows * (qkvw * 4 + hq * hd * 6 + 2 * hkv * hd * 2)
+    like_bytes = rows * (qkvw * 2 + hq * hd * 2 + 2 * hkv * hd * 2)
+    t_new = us(lambda: ops.rope_store(proj, half, hd // 2, False, pos, slot, table, qo, kp, vp, hq, hkv, hd, hd, q_half=qh, bias=bias))
+    entry("rope_store_with_biases", t_new, t_like, store_bytes, like_bytes=like_bytes, like="rope_kv_store (bfloat16 in and out)")
+    wn = rnd(hd)
+    t_new = us(lambda: ops.head_norm_store(proj, 1e-6, pos, slot, table, qo, kp, vp, hq, hkv, hd, hd, (hq + hkv) * hd, norm=True, wq=wn, wk=wn,
+                                           q_half=qh, bias=bias, temp_coef=0.1, temp_every=1024))
+    entry("head_norm_store_with_weights_biases_temperature", t_new, t_like, store_bytes, like_bytes=like_bytes,
+          like="rope_kv_store (bfloat16 in and out)")
+    del proj, proj16, qo, qo16, qh, kp, vp
+    # latent attention: norm of the query latent, then rotation, latent norm and the write of the plane
+    r, dr, rq = 4 * hd, hd // 2, 6 * hd
+    wide = r + dr
+    lproj = rnd(rows, rq + wide + hq)
+    queries = rnd(rows, hq * (hd + dr))
+    lp = torch.zeros(pages, 1, page, wide, dtype=bf, device=dev)
+    qw_, qp_ = torch.empty(rows, hq, wide, device=dev), torch.empty(rows, hq, hd, dtype=bf, device=dev)
+    wl, wq = rnd(r), rnd(rq)
+    tab = torch.zeros(4096, dr // 2, 2, device=dev)
+    cq = torch.empty(rows, rq, dtype=bf, device=dev)
+    t_new = us(lambda: (ops.gla_output(lproj[:, :rq], None, wq, 1e-6, cq, 1, rq),
+                        ops.latent_encode(lproj, rq, wl, 1e-6, tab, dr, pos, slot, table, qw_, qp_, lp, hq, hd, dr, r, queries=queries,
+                                          interleaved=False)))
+    entry("query_latent_norm_and_latent_encode", t_new, t_like,
+          rows * (rq * 6 + hq * (hd + dr) * 4 + wide * 4 + hq * dr * 4 + hq * hd * 2 + wide * 2), like_bytes=like_bytes,
+          like="rope_kv_store (bfloat16 in and out)")
+    del lproj, queries, qw_, qp_, cq
+    # latent attention with a sink over every earlier token (no window): 64 decoding rows at 4,096 tokens and one prompt of 4,096
+    ctx, b = 4096, 64
+    pages = b * ctx // page
+    table = torch.arange(pages, dtype=torch.int32, device=dev).view(b, -1).contiguous()
+    lp = rnd(pages, 1, page, wide, dt=bf)
+    sk = rnd(hq)
+    posd = torch.full((b,), ctx - 1, dtype=torch.int32, device=dev)
+    slotd = torch.arange(b, dtype=torch.int32, device=dev)
+    if ops.attention_wide_mma_supports(wide, r, wide, False):
+        q = rnd(b, hq * wide)
+        o = torch.empty(b, hq * r, dtype=bf, device=dev)
+        items = b * (-(-hq // 16))
+        splits = max(1, min(6 * ops.sm_count() // items, -(-ctx // 64), 32))
+        scratch = torch.empty(max(1, ops.attention_wide_mma_scratch_words(items, r, splits)), device=dev)
+        t_new = us(lambda: ops.attention_wide_mma(q, lp, lp, o, sk, posd, slotd, table, None, None, b, True, hq, 1, wide, r, None, 0.1, splits,
+                                                  scratch))
+        entry("latent_sink_attention_decode", t_new, nbytes=b * ctx * wide * 2, like="(no like kernel: one plane read for keys and values)")
+        n = ctx
+        posp = torch.arange(n, dtype=torch.int32, device=dev)
+        slotp = torch.zeros(n, dtype=torch.int32, device=dev)
+        qp, op = rnd(n, hq * wide), torch.empty(n, hq * r, dtype=bf, device=dev)
+        tile = ops.attention_wide_mma_tile_rows(r)
+        u0 = torch.arange(0, n, tile, dtype=torch.int32, device=dev)
+        un = torch.full_like(u0, tile)
+        t_new = us(lambda: ops.attention_wide_mma(qp, lp, lp, op, sk, posp, slotp, table, u0, un, u0.numel(), False, hq, 1, wide, r, None, 0.1),
+                   reps=2)
+        entry("latent_sink_attention_prefill", t_new, flops=2 * (n * (n + 1) // 2) * hq * (wide + r),
+              like="(no like kernel; multiply-adds of the carried form)")
+        del q, o, qp, op
+    del lp
+    # the matrix memory: gates (4,096 rows), 64 sequences of one token, one sequence of 4,096 tokens, the read-out
+    heads, dk, dv, n = max(1, hq // 2), hd, 2 * hd, 4096
+    kw, vw = heads * dk, heads * dv
+    width = 2 * kw + 2 * vw + 2 * heads
+    proj = rnd(n, width, scale=0.3)
+    state = torch.zeros(b, ops.mm_state_floats(heads, dk, dv), device=dev)
+    gates = torch.empty(n, heads, 4, device=dev)
+    bi = rnd(heads)
+    cup = torch.tensor([0, n], dtype=torch.int32, device=dev)
+    zero = torch.zeros(n, dtype=torch.int32, device=dev)
+    cu1 = torch.arange(b + 1, dtype=torch.int32, device=dev)
+    i_off, f_off = 2 * kw + 2 * vw, 2 * kw + 2 * vw + heads
+    t_new = us(lambda: ops.mm_gates(proj, i_off, f_off, bi, bi, 15.0, state, cup, zero[:1], zero, gates, 1, heads, dk, dv))
+    gproj = rnd(n, 2 * kw + 2 * vw + 16, scale=0.1)
+    w2 = rnd(kw, 16, dt=bf)
+    dec = torch.empty(n, kw, device=dev)
+    t_like = us(lambda: ops.gla_decay(gproj[:, 2 * kw + 2 * vw:], w2, None, 16.0, dec))
+    entry("mm_gates_one_sequence", t_new, t_like, n * heads * (8 + 16), like_bytes=n * (16 * 4 + kw * 4),
+          like="gla_decay (what the gated linear attention computes before its scan)")
+    t_new = us(lambda: ops.mm_gates(proj[:b], i_off, f_off, bi, bi, 15.0, state, cu1, slotd, slotd, gates[:b], b, heads, dk, dv))
+    entry("mm_gates_decode", t_new, nbytes=b * heads * (8 + 16 + 8))
+    og = torch.empty(n, heads, dv + 1, device=dev)
+    t_new = us(lambda: ops.mm_scan(proj[:b], 0, kw, 2 * kw, gates[:b], 0.1, state, cu1, slotd, slotd, og[:b], b, heads, dk, dv))
+    gstate = torch.zeros(b, heads, dk, dv, device=dev)
+    gout = torch.empty(n, vw, device=dev)
+    dec.uniform_(0.9, 1.0)
+    t_like = us(lambda: ops.gla_scan(gproj[:b], 0, kw, 2 * kw, dec[:b], 0.1, gstate, cu1, slotd, slotd, gout[:b], b, heads, dk, dv))
+    entry("mm_scan_decode", t_new, t_like, 2 * b * heads * dk * (dv + 1) * 4, like_bytes=2 * b * heads * dk * dv * 4, like="gla_scan (decode)")
+    t_new = us(lambda: ops.mm_scan(proj, 0, kw, 2 * kw, gates, 0.1, state, cup, zero[:1], zero, og, 1, heads, dk, dv, narrow=True), reps=2)
+    t_like = us(lambda: ops.gla_scan(gproj, 0, kw, 2 * kw, dec, 0.1, gstate, cup, zero[:1], zero, gout, 1, heads, dk, dv, narrow=True), reps=2)
+    # (CUDA-core multiply-adds, the scan is sequential: two products of the state a token in both)
+    entry("mm_scan_prefill", t_new, t_like, flops=n * heads * dk * (dv + 1) * 4, like_flops=n * heads * dk * dv * 4, like="gla_scan (one prompt)")
+    y = torch.empty(n, vw, dtype=bf, device=dev)
+    normw, normd = rnd(vw), rnd(dv)
+    t_new = us(lambda: ops.mm_output(og, gates, proj[:, 2 * kw + vw:2 * kw + 2 * vw], normw, 1e-6, y, heads, dv))
+    t_like = us(lambda: ops.gla_output(gout, gproj[:, 2 * kw + vw:2 * kw + 2 * vw], normd, 1e-6, y, heads, dv))
+    entry("mm_output", t_new, t_like, n * (vw * (4 + 4 + 2) + heads * 20), like_bytes=n * vw * (4 + 4 + 2), like="gla_output")
+    return out
+
+
+def workload_varolix(a, pk):
+    """The Varolix design at the layer sizes of the Qwen2.5 shapes, beside the Fozutar design (the closest one: attention
+    layers, layers with a matrix state, dense feed-forwards) and the dense decoder at the same sizes: decode at the headline
+    batch and context, one prompt of `--prefill` tokens, and the new kernels alone."""
+    import torch
+
+    from machserve_b200 import ops
+
+    out = {}
+    shapes = sorted(SHAPES) if a.varolix_shapes == "all" else [x.strip() for x in a.varolix_shapes.split(",") if x.strip()]
+    for shape in shapes:
+        raw = SHAPES[shape]
+        layers = min(raw["num_hidden_layers"], a.layers or 12)  # (layers of like sizes: twelve tell what all tell)
+        res = {"layers": layers}
+        steps = max(10, a.steps // 2)
+        for which in ("varolix", "fozutar", "dense"):
+            kw = {}
+            if which != "dense":
+                kw = dict(config=(varolix_config if which == "varolix" else fozutar_config)(raw, layers), vocab=raw["vocab_size"])
+            b = DecodeBench(a, raw, layers, "bf16", a.batch, a.context + 4 * (steps + a.warmup) + a.batch + 64, **kw)
+            times, launches = b.time_decode(a.batch, a.context, steps, a.warmup, blocks=3, sampled=False)
+            pms = b.time_prefill(a.prefill, 2, reps=3)
+            res[which] = {"decode_ms_per_step": round(times[len(times) // 2], 4), "decode_tokens_per_s": round(a.batch * 1000.0 / times[len(times) // 2], 1),
+                          "launches_per_step": launches // steps, "prefill_ms": round(pms, 3), "prefill_tokens_per_s": round(a.prefill * 1000.0 / pms, 1)}
+            b.runner.check_device_status()
+            b.release_all()
+            del b
+            free_device_memory()
+        if not a.no_points:
+            res["kernels"] = time_varolix_kernels(torch, ops, raw, pk)
+        free_device_memory()
+        out[shape] = res
+    return {"batch": a.batch, "context": a.context, "prefill_tokens": a.prefill, "dtype": "bf16",
+            "data": "random-init weights drawn on the device, seeded uniform random token ids", "peaks": pk["source"], "sizes": out}
+
+
 def workload_serving(a, pk):
     """Qwen2.5-1.5B sizes: 64 requests, prompts of 128 to 2,048 tokens (seeded), 256 new tokens each, through `Engine`
     with its default budget of prompt tokens per step.  All requests arrive at time zero.  Three loads of other prompt
@@ -1333,11 +1554,13 @@ def main() -> int:
                     help="which parts to run: headline, fp32, serving_1p5b, mixed_7b (comma separated); venarax, which is not "
                          "among the defaults, times the Venarax design beside the dense decoder at equal layer sizes; fozutar, "
                          "likewise not among the defaults, does the same for the Fozutar design; modadra, not among the defaults "
-                         "either, times the Modadra design beside the Fozutar design and the dense decoder")
+                         "either, times the Modadra design beside the Fozutar design and the dense decoder; varolix, not among the defaults "
+                         "either, does the same for the Varolix design")
     ap.add_argument("--no-points", action="store_true", help="skip the further batch sizes and the prefill (venarax: the kernels alone)")
     ap.add_argument("--venarax-shapes", default="all", help="the shapes of the venarax workload (comma separated), or all")
     ap.add_argument("--fozutar-shapes", default="all", help="the shapes of the fozutar workload (comma separated), or all")
     ap.add_argument("--modadra-shapes", default="all", help="the shapes of the modadra workload (comma separated), or all")
+    ap.add_argument("--varolix-shapes", default="all", help="the shapes of the varolix workload (comma separated), or all")
     ap.add_argument("--profile", default=None, choices=["decode", "prefill", "mixed"],
                     help="which timed region is bracketed by cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     ap.add_argument("--kernel", default=None, choices=["attention_prefill", "gemm"],
@@ -1457,6 +1680,8 @@ def main() -> int:
         line["fozutar"] = workload_fozutar(a, pk)
     if "modadra" in only:
         line["modadra"] = workload_modadra(a, pk)
+    if "varolix" in only:
+        line["varolix"] = workload_varolix(a, pk)
     print(json.dumps(line))
     return 0
 

@@ -12,9 +12,10 @@
 // A request's slot holds, per head, the matrix with the normalizer as one more column ([heads, dk, dv + 1]: n is the
 // state of a value that is always 1) and, behind all matrices, the heads' m.
 //
-// mm_gates:   a block owns one head of one sequence.  128 rows at a time: every thread makes the two gates of its row, one
-//             thread walks the chain m (an add and a max a row), every thread makes a_t and b_t of its row from the two m
-//             beside it.  Leaves [a, b, m, 0] per (row, head) and the slot's new m.
+// mm_gates:   a block owns one head of one sequence.  1,024 rows at a time: the threads make the two gates of their rows, one
+//             thread walks the chain m (an add and a max a row, in the rows' order, so that m does not depend on how the
+//             sequence was cut), the threads make a_t and b_t of their rows from the two m beside them.  Leaves [a, b, m, 0]
+//             per (row, head) and the slot's new m.
 // mm_scan:    a block owns 32 (or 8) columns of [S | n] of one head of one sequence and goes through the sequence's rows of
 //             the step in order, from the state the step found to the state it leaves.  Thread (c, g) holds KPT consecutive
 //             key rows of column c in registers; q, k, a and b of TB rows at a time are staged in shared memory, the next
@@ -26,14 +27,15 @@
 
 #define MM_GROUPS 16
 #define MM_TB 16
-#define MM_CHUNK 128
+#define MM_CHUNK 1024
+#define MM_GATE_THREADS 128
 
-__global__ void __launch_bounds__(MM_CHUNK)
+__global__ void __launch_bounds__(MM_GATE_THREADS)
 mm_gates_kernel(const float* __restrict__ proj, int ld, int i_off, int f_off, const float* __restrict__ bias_i,
                 const float* __restrict__ bias_f, float cap, float* __restrict__ state, long long slot_stride, long long m_off,
                 const int* __restrict__ cu_tokens, const int* __restrict__ state_slots, const int* __restrict__ slot_of_token,
                 float* __restrict__ gates, int heads) {
-  __shared__ float si[MM_CHUNK], sf[MM_CHUNK], sm[MM_CHUNK + 1];
+  __shared__ __align__(16) float si[MM_CHUNK], sf[MM_CHUNK], sm[MM_CHUNK + 4];
   ms_pdl_trigger();
   ms_pdl_wait();
   const int h = blockIdx.x, seq = blockIdx.y;
@@ -43,25 +45,31 @@ mm_gates_kernel(const float* __restrict__ proj, int ld, int i_off, int f_off, co
   const float bi = bias_i ? bias_i[h] : 0.f, bf = bias_f ? bias_f[h] : 0.f;
   const float inv_cap = 1.f / cap;
   float m = threadIdx.x == 0 ? *mp : 0.f;
-  const int j = threadIdx.x;
   for (int t0 = 0; t0 < rows; t0 += MM_CHUNK) {
     const int nt = min(MM_CHUNK, rows - t0);
-    if (j < nt) {
+    for (int j = threadIdx.x; j < nt; j += MM_GATE_THREADS) {
       const float* r = proj + (size_t)(row0 + t0 + j) * ld;
       si[j] = cap * tanhf((r[i_off + h] + bi) * inv_cap);
       const float z = cap * tanhf((r[f_off + h] + bf) * inv_cap);
       sf[j] = fminf(z, 0.f) - log1pf(expf(-fabsf(z)));
     }
     __syncthreads();
-    if (j == 0) {
+    if (threadIdx.x == 0) {  // the chain: an add and a max a row, in the rows' order; the loads run ahead of it
       sm[0] = m;
-      for (int e = 0; e < nt; ++e) {
+      int e = 0;
+      for (; e + 4 <= nt; e += 4) {
+        const float4 f4 = *reinterpret_cast<const float4*>(sf + e), i4 = *reinterpret_cast<const float4*>(si + e);
+        const float m0 = fmaxf(f4.x + m, i4.x), m1 = fmaxf(f4.y + m0, i4.y), m2 = fmaxf(f4.z + m1, i4.z), m3 = fmaxf(f4.w + m2, i4.w);
+        sm[e + 1] = m0, sm[e + 2] = m1, sm[e + 3] = m2, sm[e + 4] = m3;
+        m = m3;
+      }
+      for (; e < nt; ++e) {
         m = fmaxf(sf[e] + m, si[e]);
         sm[e + 1] = m;
       }
     }
     __syncthreads();
-    if (j < nt) {
+    for (int j = threadIdx.x; j < nt; j += MM_GATE_THREADS) {
       const float before = sm[j], now = sm[j + 1];
       float4 g;
       g.x = expf(sf[j] + before - now);
@@ -72,7 +80,7 @@ mm_gates_kernel(const float* __restrict__ proj, int ld, int i_off, int f_off, co
     }
     __syncthreads();
   }
-  if (j == 0) *mp = m;
+  if (threadIdx.x == 0) *mp = m;
 }
 
 // proj float32 [T, ld]: the input gates' pre-activations at columns i_off + h, the forget gates' at f_off + h; biases float32
@@ -85,7 +93,7 @@ MS_API int ms_mm_gates(const float* proj, int ld, int i_off, int f_off, const fl
              "mm_gates: bad arguments seqs=%d heads=%d cap=%g ld=%d", seqs, heads, cap, ld);
   MS_REQUIRE(seqs <= 65535, "mm_gates: too many sequences for one launch");
   MS_REQUIRE(((uintptr_t)gates) % 16 == 0, "mm_gates: the gates' rows must lie on 16-byte boundaries");
-  MS_LAUNCH_RESULT("mm_gates", ms_launch(mm_gates_kernel, dim3(heads, seqs), dim3(MM_CHUNK), 0, stream, 1, true, proj, ld, i_off, f_off,
+  MS_LAUNCH_RESULT("mm_gates", ms_launch(mm_gates_kernel, dim3(heads, seqs), dim3(MM_GATE_THREADS), 0, stream, 1, true, proj, ld, i_off, f_off,
                                          bias_i, bias_f, cap, state, slot_stride, m_off, cu_tokens, state_slots, slot_of_token, gates,
                                          heads));
   return 0;
