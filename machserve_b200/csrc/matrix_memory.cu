@@ -47,11 +47,22 @@ mm_gates_kernel(const float* __restrict__ proj, int ld, int i_off, int f_off, co
   float m = threadIdx.x == 0 ? *mp : 0.f;
   for (int t0 = 0; t0 < rows; t0 += MM_CHUNK) {
     const int nt = min(MM_CHUNK, rows - t0);
-    for (int j = threadIdx.x; j < nt; j += MM_GATE_THREADS) {
-      const float* r = proj + (size_t)(row0 + t0 + j) * ld;
-      si[j] = cap * tanhf((r[i_off + h] + bi) * inv_cap);
-      const float z = cap * tanhf((r[f_off + h] + bf) * inv_cap);
-      sf[j] = fminf(z, 0.f) - log1pf(expf(-fabsf(z)));
+    float xi[MM_CHUNK / MM_GATE_THREADS], xf[MM_CHUNK / MM_GATE_THREADS];
+#pragma unroll
+    for (int u = 0; u < MM_CHUNK / MM_GATE_THREADS; ++u) {  // every load of the round is requested before the first is used
+      const int j = threadIdx.x + u * MM_GATE_THREADS;
+      const float* r = proj + (size_t)(row0 + t0 + (j < nt ? j : 0)) * ld;
+      xi[u] = r[i_off + h];
+      xf[u] = r[f_off + h];
+    }
+#pragma unroll
+    for (int u = 0; u < MM_CHUNK / MM_GATE_THREADS; ++u) {
+      const int j = threadIdx.x + u * MM_GATE_THREADS;
+      if (j < nt) {
+        si[j] = cap * tanhf((xi[u] + bi) * inv_cap);
+        const float z = cap * tanhf((xf[u] + bf) * inv_cap);
+        sf[j] = fminf(z, 0.f) - log1pf(expf(-fabsf(z)));
+      }
     }
     __syncthreads();
     if (threadIdx.x == 0) {  // the chain: an add and a max a row, in the rows' order; the loads run ahead of it

@@ -146,7 +146,8 @@ def test_head_norms_with_a_shared_weight_biases_and_the_temperature(hq, hkv, dk,
 
 
 @pytest.mark.parametrize("heads,dn,dr,r,rot,interleaved,page", [(3, 8, 4, 16, 4, False, 8), (1, 5, 6, 9, 4, False, 16), (4, 32, 16, 48, 16, False, 16),
-                                                                (2, 16, 8, 20, 8, True, 8), (5, 4, 2, 8, 2, False, 16)])
+                                                                (2, 16, 8, 20, 8, True, 8), (5, 4, 2, 8, 2, False, 16), (2, 64, 32, 256, 32, False, 16),
+                                                                (3, 16, 16, 32, 8, False, 8)])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_latent_norm_rotation_in_halves_and_queries_from_a_product_of_their_own(heads, dn, dr, r, rot, interleaved, page, dtype):
     torch = _torch()
@@ -156,9 +157,12 @@ def test_latent_norm_rotation_in_halves_and_queries_from_a_product_of_their_own(
     tdt = torch.float32 if dtype == "float32" else torch.bfloat16
     positions = [0, 1, 7, 8, 16, 37, 90]
     n, hd, wide = len(positions), dn + dr, r + dr
-    lead = 6  # the columns ahead of the down-projection in the input product: the queries' own latent
-    proj = rng.normal(size=(n, lead + wide + heads)).astype(np.float32)
-    queries = rng.normal(size=(n, heads * hd + 2)).astype(np.float32)
+    # the columns ahead of the down-projection in the input product (the queries' own latent) and the rows' lengths: on
+    # 16-byte boundaries where the sizes allow the kernel's 16-byte form, off them otherwise
+    by4 = dn % 4 == 0 and dr % 4 == 0 and r % 4 == 0 and rot % 8 == 0 and not interleaved
+    lead = 8 if by4 else 6
+    proj = rng.normal(size=(n, -(-(lead + wide + heads) // 4) * 4 if by4 else lead + wide + heads)).astype(np.float32)
+    queries = rng.normal(size=(n, heads * hd + (4 if by4 else 2))).astype(np.float32)
     w = (1 + 0.2 * rng.normal(size=r)).astype(np.float32)
     cos_sin = _table(rot, 50.0, None)
     pp, table = _paged(rng, [91], 1, wide, page)
