@@ -658,6 +658,34 @@ def test_unequal_requests_side_by_side_on_reused_pages_and_slots(model_root, nam
             assert_close(got[rid], alone[rid], 2e-6, f"float32 logits of {rid} must not depend on the batch, the pages or the slot")
 
 
+@pytest.mark.parametrize("seed", range(16))
+def test_configurations_drawn_from_many_sizes(model_root, seed):
+    """Sixteen configurations drawn from many sizes (head counts, groups, widths inside and outside what the tensor-core
+    kernels cover, ranks, rotations, layer orders, loops): a prompt of 130 rows and 20 rows decoded one by one, in both dtypes,
+    against the plain model.  The typical row within float32's and bfloat16's rounding; no row far off (a row of a matrix
+    memory whose live terms cancel may be off by more than the typical one: see `plain_with_reach`)."""
+    import torch
+
+    from machserve_b200.config import config_from_json
+    from machserve_b200.weights import write_random_model
+    from tests.varolix_cases import random_case
+
+    raw = random_case(seed)
+    d = model_root / f"varolix_drawn_{seed}"
+    if not (d / "model.safetensors").exists():
+        write_random_model(config_from_json(raw), d, seed, torch.bfloat16, 0.06, 0.2, 0.1)
+    toks = random_tokens(raw["vocab"], 150, seed)
+    want = plain_logits(d, toks)
+    spread = np.sqrt(((want - want.mean(-1, keepdims=True)) ** 2).mean())
+    steps = trace_tail_decode("a", toks, 20)
+    for dtype, typical, far in (("float32", 2e-5, 2e-3), ("bfloat16", 6e-2, 1.0)):
+        got = collect_rows(steps, _replay(d, dtype, steps, 192, 16))["a"]
+        assert np.isfinite(got).all()
+        diff = got - want
+        err = np.sqrt(((diff - diff.mean(-1, keepdims=True)) ** 2).mean(-1)) / spread
+        assert np.median(err) < typical and err.max() < far, f"seed {seed} {dtype}: median {np.median(err):.3g}, largest {err.max():.3g} at row {int(err.argmax())}"
+
+
 @pytest.mark.parametrize("name", ["D", "A"])
 def test_long_decoding_from_a_short_prompt(model_root, name):
     """Four tokens of prompt and then 180 tokens one by one, in float32: the memories (lasting ones in D) and the caches pass

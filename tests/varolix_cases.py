@@ -94,6 +94,47 @@ CASES = {
 }
 
 
+def random_case(seed: int) -> dict:
+    """A configuration drawn from many sizes: widths, head counts and groups, key and value widths that the tensor-core kernels
+    cover and that they do not, rotations of all, a part and none of a head with and without stretching, latents of many ranks,
+    two to six layers of the three kinds in any order, with and without a loop."""
+    import random
+
+    rng = random.Random(seed)
+
+    def att():
+        dim = rng.choice([16, 32, 48, 64, 80, 96, 128, 192, 256])
+        kv, g = rng.choice([1, 2, 3, 4]), rng.choice([1, 2, 3, 4, 8])
+        dims = rng.choice([dim, dim // 2, dim // 4 * 2, 8, 0]) // 2 * 2
+        scaling = None
+        if dims and rng.random() < 0.7:
+            scaling = (rng.choice([2.0, 8.0, 32.0]), rng.choice([16, 64, 1024, 4096]), rng.choice([32.0, 8.0, 4.0]), rng.choice([1.0, 0.5, 2.0]))
+        return _attention(kv * g, kv, dim, rng.choice([dim, dim, 32, 64, 128, 40]), dim ** -0.5 * rng.choice([1.0, 0.7, 1.3]),
+                          (dims, rng.choice([100.0, 10000.0, 50000.0, 1e6])) if dims else None, scaling)
+
+    def pair():
+        dim = rng.choice([16, 32, 48, 64, 96, 128])
+        kv, g = rng.choice([1, 2, 3]), rng.choice([1, 2, 4, 6])
+        left = (kv * g, kv, dim, rng.choice([dim, 32, 64, 128, 24]), rng.choice([0.125, dim ** -0.5, 0.3]),
+                (rng.choice([0.5, 0.1, 1.0]), rng.choice([1, 7, 32, 128])))
+        right = (rng.choice([1, 2, 3, 4]), rng.choice([8, 16, 24, 48, 64, 100, 128]), rng.choice([8, 16, 33, 64, 96, 128]), rng.choice([15.0, 5.0, 30.0]))
+        return _pair(left, right, rng.choice([1.2, 1.0, 0.5]), rng.choice([0.9, 1.0, 1.5]))
+
+    def lat():
+        dim, rd = rng.choice([16, 32, 64, 96, 128]), rng.choice([8, 16, 32, 64, 24])
+        return _latent(rng.choice([1, 2, 4, 8, 12, 16, 20]), dim, rd, rng.choice([dim, 32, 64, 48]), rng.choice([32, 64, 128, 192, 256, 72]),
+                       rng.choice([24, 80, 96, 200]), (dim + rd) ** -0.5, rng.choice([50000.0, 10000.0]))
+
+    width = rng.choice([64, 96, 160, 192, 320, 384])
+    n = rng.choice([2, 3, 4, 6])
+    layers = [_with(rng.choice([att, pair, lat])(), rng.choice([64, 256, 200]) if rng.random() < 0.85 else None) for _ in range(n)]
+    loop = None
+    if rng.random() < 0.7:
+        a = rng.randrange(0, n)
+        loop = (a, rng.randrange(a + 1, n + 1), rng.choice([1, 2, 3]))
+    return _config(rng.choice([100, 576, 1000, 257]), width, rng.choice([1e-6, 1e-5]), layers, loop)
+
+
 def make_model_dir(root, name: str) -> Path:
     """Writes the tiny model `name` (config.json, model.safetensors in bfloat16-exact float32) under root."""
     import torch
