@@ -1165,7 +1165,7 @@ def varolix_config(raw, layers):
     att = {"heads": hq, "kv_heads": hkv, "dim": hd, "vdim": hd, "scale": hd ** -0.5,
            "rot": {"dims": hd // 2, "base": 10000.0, "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}
     pair = {"left": {"heads": hq, "kv_heads": hkv, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "q_temp": {"coef": 0.1, "every": 1024}},
-            "right": {"heads": max(1, hq // 2), "dim": hd, "vdim": 2 * hd, "gate_cap": 15.0}, "left_scale": 1.0, "right_scale": 0.5}
+            "right": {"heads": max(1, hq // 2), "dim": hd, "vdim": 2 * hd, "gate_cap": 12.0}, "left_scale": 1.0, "right_scale": 0.5}
     lat = {"heads": hq, "dim": hd, "rot_dim": hd // 2, "vdim": hd, "kv_rank": 4 * hd, "q_rank": 6 * hd, "scale": (1.5 * hd) ** -0.5,
            "rot": {"dims": hd // 2, "base": 10000.0}}
     kinds = [("attention", att), ("parallel", pair), ("latent_attention", lat)]

@@ -54,13 +54,13 @@ CASES = {
     "A": dict(config=_config(150, 64, 1e-5, [
         _with(_attention(4, 2, 16, 24, 0.3, (8, 100.0), (4.0, 32, 8.0, 1.0)), 48),
         _with(_pair((4, 2, 16, 8, 0.35, (0.3, 5)), (2, 8, 12, 4.0), 0.7, 1.3), None),
-        _with(_latent(3, 8, 4, 12, 16, 10, 0.28, 100.0), 40),
+        _with(_latent(3, 8, 4, 12, 16, 10, 0.28, 300.0), 40),
         _with(_attention(2, 2, 8, 8, 0.4, (8, 30.0)), 24),
     ], loop=(1, 3, 3)), seed=41, page=8),
     # odd sizes everywhere; no loop, no temperature, no stretching; one head for all keys; a latent wider than a head; a rotation
     # of a part of the rotated coordinates
     "B": dict(config=_config(131, 50, 1e-6, [
-        _with(_pair((3, 3, 10, 7, 0.31, None), (3, 7, 9, 15.0), 1.0, 1.0), 21),
+        _with(_pair((3, 3, 10, 7, 0.31, None), (3, 7, 9, 11.0), 1.0, 1.0), 21),
         _with(_attention(5, 1, 6, 5, 0.45, (2, 7.0)), 37),
         _with(_latent(1, 5, 6, 3, 9, 7, 0.5, 13.0, 4), None),
         _with(_pair((2, 1, 6, 11, 0.4, (0.9, 1)), (1, 5, 3, 2.5), -0.8, 0.6), 33),
@@ -69,7 +69,7 @@ CASES = {
     # cluster kernel); the first two layers run twice
     "C": dict(config=_config(128, 96, 1e-6, [
         _with(_attention(4, 1, 64, 64, 0.12, (32, 10000.0), (4.0, 64, 16.0, 2.0)), 64),
-        _with(_pair((2, 2, 64, 64, 0.125, (0.5, 16)), (2, 32, 64, 15.0), 1.2, 0.9), 128),
+        _with(_pair((2, 2, 64, 64, 0.11, (0.6, 16)), (2, 32, 64, 12.0), 1.25, 0.75), 128),
         _with(_latent(4, 32, 16, 32, 48, 24, 0.14, 5000.0), 64),
         _with(_attention(2, 2, 128, 128, 0.09, (128, 500.0)), 96),
         _with(_pair((4, 1, 32, 32, 0.17, (0.2, 40)), (1, 64, 32, 8.0), 0.5, 1.5), 64),
@@ -110,29 +110,29 @@ def random_case(seed: int) -> dict:
         if dims and rng.random() < 0.7:
             scaling = (rng.choice([2.0, 8.0, 32.0]), rng.choice([16, 64, 1024, 4096]), rng.choice([32.0, 8.0, 4.0]), rng.choice([1.0, 0.5, 2.0]))
         return _attention(kv * g, kv, dim, rng.choice([dim, dim, 32, 64, 128, 40]), dim ** -0.5 * rng.choice([1.0, 0.7, 1.3]),
-                          (dims, rng.choice([100.0, 10000.0, 50000.0, 1e6])) if dims else None, scaling)
+                          (dims, rng.choice([100.0, 10000.0, 40000.0, 1e6])) if dims else None, scaling)
 
     def pair():
         dim = rng.choice([16, 32, 48, 64, 96, 128])
         kv, g = rng.choice([1, 2, 3]), rng.choice([1, 2, 4, 6])
-        left = (kv * g, kv, dim, rng.choice([dim, 32, 64, 128, 24]), rng.choice([0.125, dim ** -0.5, 0.3]),
-                (rng.choice([0.5, 0.1, 1.0]), rng.choice([1, 7, 32, 128])))
-        right = (rng.choice([1, 2, 3, 4]), rng.choice([8, 16, 24, 48, 64, 100, 128]), rng.choice([8, 16, 33, 64, 96, 128]), rng.choice([15.0, 5.0, 30.0]))
-        return _pair(left, right, rng.choice([1.2, 1.0, 0.5]), rng.choice([0.9, 1.0, 1.5]))
+        left = (kv * g, kv, dim, rng.choice([dim, 32, 64, 128, 24]), rng.choice([0.11, dim ** -0.5, 0.3]),
+                (rng.choice([0.6, 0.1, 1.0]), rng.choice([1, 7, 32, 100])))
+        right = (rng.choice([1, 2, 3, 4]), rng.choice([8, 16, 24, 48, 64, 100, 128]), rng.choice([8, 16, 33, 64, 96, 128]), rng.choice([12.0, 5.0, 30.0]))
+        return _pair(left, right, rng.choice([1.25, 1.0, 0.5]), rng.choice([0.75, 1.0, 1.5]))
 
     def lat():
         dim, rd = rng.choice([16, 32, 64, 96, 128]), rng.choice([8, 16, 32, 64, 24])
         return _latent(rng.choice([1, 2, 4, 8, 12, 16, 20]), dim, rd, rng.choice([dim, 32, 64, 48]), rng.choice([32, 64, 128, 192, 256, 72]),
-                       rng.choice([24, 80, 96, 200]), (dim + rd) ** -0.5, rng.choice([50000.0, 10000.0]))
+                       rng.choice([24, 72, 96, 200]), (dim + rd) ** -0.5, rng.choice([40000.0, 10000.0]))
 
-    width = rng.choice([64, 96, 160, 192, 320, 384])
+    width = rng.choice([64, 96, 160, 192, 288, 384])
     n = rng.choice([2, 3, 4, 6])
     layers = [_with(rng.choice([att, pair, lat])(), rng.choice([64, 256, 200]) if rng.random() < 0.85 else None) for _ in range(n)]
     loop = None
     if rng.random() < 0.7:
         a = rng.randrange(0, n)
         loop = (a, rng.randrange(a + 1, n + 1), rng.choice([1, 2, 3]))
-    return _config(rng.choice([100, 576, 1000, 257]), width, rng.choice([1e-6, 1e-5]), layers, loop)
+    return _config(rng.choice([100, 512, 1000, 257]), width, rng.choice([1e-6, 1e-5]), layers, loop)
 
 
 def make_model_dir(root, name: str) -> Path:
