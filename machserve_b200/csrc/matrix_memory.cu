@@ -303,17 +303,17 @@ mm_output_kernel(const float* __restrict__ o, const float* __restrict__ gates, c
   if (item >= items) return;
   const int t = item / heads, h = item - t * heads;
   const float* x = o + (size_t)item * (dv + 1);
-  const float den = fmaxf(fabsf(x[dv]), expf(-gates[(size_t)item * 4 + 2])) + 1e-6f;
+  const float inv_den = 1.f / (fmaxf(fabsf(x[dv]), expf(-gates[(size_t)item * 4 + 2])) + 1e-6f);  // one division a (row, head)
   float ss = 0.f;
   for (int d = lane; d < dv; d += 32) {
-    const float y = x[d] / den;
+    const float y = x[d] * inv_den;
     ss += y * y;
   }
   ss = ms_warp_sum(ss);
-  const float inv = 1.f / sqrtf(ss / (float)dv + eps);
+  const float inv = inv_den / sqrtf(ss / (float)dv + eps);
   const float* gr = gate ? gate + (size_t)t * ldg + (size_t)h * dv : nullptr;
   for (int d = lane; d < dv; d += 32) {
-    float y = x[d] / den * inv * (w ? w[(size_t)h * dv + d] : 1.f);
+    float y = x[d] * inv * (w ? w[(size_t)h * dv + d] : 1.f);
     if (gr) y *= 1.f / (1.f + expf(-gr[d]));
     out[((size_t)t * heads + h) * dv + d] = ms_from_float<TO>(y);
   }
